@@ -26,6 +26,17 @@ class RMSNormSpec:
 
 
 @dataclass(frozen=True)
+class RMSGainsSpec:
+    """One RMS statistic, several gains: y_k = x / sqrt(mean(x^2) + eps) * gain_k for every name in ``names`` (the
+    gains' local tensor names; an empty name is the norm's prefix alone).  The sublayers of a layer that all read
+    the same residual through norms of their own get their inputs from one pass over it."""
+    size: int
+    eps: float
+    names: Tuple[str, ...] = ("",)
+    kind: str = "rms_gains"
+
+
+@dataclass(frozen=True)
 class LayerNormSpec:
     """y = (x - mean) / sqrt(var + eps) * gain (+ bias) over ``size`` elements, var the mean squared deviation.
 
@@ -46,11 +57,16 @@ class RopePairsSpec:
     ``yarn`` (None for none) holds (factor, original, fast, slow): with
     d(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(d(fast)), 0),
     hi = min(ceil(d(slow)), rotary_dim - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1) the frequency is
-    f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos and sin are both multiplied by 0.1 ln(factor) + 1."""
+    f_i / factor * ramp_i + f_i * (1 - ramp_i), and cos and sin are both multiplied by 0.1 ln(factor) + 1.
+
+    ``by_wavelength`` (None for none) holds (factor, low, high, original): with the wavelength w_i = 2 pi / f_i a
+    frequency stays as it is where w_i < original / high, becomes f_i / factor where w_i > original / low, and between
+    the two is (1 - s) f_i / factor + s f_i with s = (original / w_i - low) / (high - low).  At most one of the two."""
     rotary_dim: int
     theta: float
     yarn: Optional[Tuple[float, float, float, float]] = None
     kind: str = "rope_pairs"
+    by_wavelength: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclass(frozen=True)
@@ -88,6 +104,13 @@ class AttentionSpec:
     term per head in the softmax's denominator, with no key and no value.  ``v_head_dim`` > 0: values (and the
     heads' outputs) have that size instead of ``head_dim``.  ``names``: the tensors' local names as
     (q, k, v, o, sink) where they are not the default ones.
+
+    ``bias``: which of the projections "q", "k", "v" have a bias (tensor: the matrix's name plus ``bias_suffix``).
+    ``values``: "own" (a projection of their own) or "keys" (the values are the keys as cached: no v tensor, one pool).
+    ``unit_rms``: queries and keys are divided by their root mean square over the head (eps ``unit_eps``, no gain)
+    AFTER the position encoding.  ``softcap`` > 0: score <- softcap * tanh(score / softcap) after the scale.
+    ``gate``: "element" multiplies the heads' outputs element by element with the sigmoid of a projection of the
+    mixer's input (tensor ``gate_name``) before the output projection; "" for none.
     """
     hidden_size: int
     num_heads: int
@@ -102,6 +125,14 @@ class AttentionSpec:
     sink: bool = False
     v_head_dim: int = 0
     names: Tuple[str, ...] = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "sink")
+    bias: Tuple[str, ...] = ()
+    bias_suffix: str = ".b"
+    values: str = "own"
+    unit_rms: bool = False
+    unit_eps: float = 0.0
+    softcap: float = 0.0
+    gate: str = ""
+    gate_name: str = "g"
 
 
 @dataclass(frozen=True)
@@ -257,11 +288,13 @@ class PairHashEmbeddingSpec:
 
 @dataclass(frozen=True)
 class HeadSpec:
-    """logits = x W^T * scale in float32, no bias, no soft-cap; W may be the embedding table (tied)."""
+    """logits = x W^T * scale in float32, no bias; W may be the embedding table (tied).  ``softcap`` > 0:
+    logits <- softcap * tanh(logits / softcap) afterwards."""
     vocab_size: int
     hidden_size: int
     kind: str = "linear"
     scale: float = 1.0
+    softcap: float = 0.0
 
 
 @dataclass(frozen=True)
@@ -322,15 +355,46 @@ class ParallelLayerSpec:
 
 
 @dataclass(frozen=True)
+class ParallelNormsLayerSpec:
+    """One block whose mixer and feed-forward (``ffn`` None: none) read the SAME residual, each through a gain of its
+    own over the one RMS statistic (``norms``: an :class:`RMSGainsSpec` with one name per sublayer), and whose outputs
+    join the residual together through ``link``: x <- x + (mixer(n1(x)) + ffn(n2(x))) (``arrangement``
+    "parallel_norms").  ``names`` maps the parts ("norms", "mixer", "ffn", "link") to the prefixes of their tensors."""
+    mixer: object
+    norms: object
+    link: object
+    ffn: object = None
+    names: Tuple[Tuple[str, str], ...] = ()
+    arrangement: str = "parallel_norms"
+
+    def prefix(self, part: str) -> str:
+        return dict(self.names).get(part, "")
+
+
+@dataclass(frozen=True)
+class PassEntrySpec:
+    """What joins the residual right before the first layer of a pass over a repeated run of layers: the embedding's
+    output once more (``readd_embedding``, for every pass but the first) and then row t of the tensor ``name``
+    [passes, hidden] for pass t (every pass)."""
+    passes: int
+    hidden_size: int
+    readd_embedding: bool = True
+    name: str = "loop.step"
+    kind: str = "pass_entry"
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One execution of a layer.  ``layer`` indexes ``ModelSpec.layers``;
     ``cache`` names the cache entry (an index into the list of cache entries)
     that this execution reads, and ``writes`` says whether it also appends to
     it.  Two entries may name the same layer (weights shared) or the same cache
-    (a layer that reads what another layer wrote)."""
+    (a layer that reads what another layer wrote).  ``enters`` >= 0: this execution is the first of pass
+    ``enters`` over a repeated run, and the model's ``pass_entry`` part adds its terms to the residual right before it."""
     layer: int
     cache: int
     writes: bool = True
+    enters: int = -1
 
 
 @dataclass(frozen=True)
@@ -357,6 +421,9 @@ class ModelSpec:
     # tensors of the embedding or the head whose names do not derive from ``embedding_name`` / ``head_name``:
     # (local name, full name) pairs
     end_names: Tuple[Tuple[str, str], ...] = ()
+    # what a pass over a repeated run of layers adds on entry (a :class:`PassEntrySpec`; None: nothing); the
+    # schedule entries with ``enters`` >= 0 say where
+    pass_entry: object = None
 
     def embedding_record(self):
         return self.embedding or EmbeddingSpec(self.vocab_size, self.hidden_size)

@@ -35,6 +35,7 @@
 // Formula: thanhauco/rust-inference src/attention.rs:111-150.
 #include "common.cuh"
 #include "mma_helpers.cuh"
+#include "softcap.cuh"
 #include <cuda.h>
 #include <float.h>
 
@@ -109,7 +110,8 @@ __global__ void __launch_bounds__(32 * AD_WARPS)
 attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_pool, const bf16* __restrict__ v_pool,
                         float* __restrict__ o_part, float* __restrict__ ml_part, const int* __restrict__ page_table,
                         const int* __restrict__ seq_slot, const int* __restrict__ seq_len, int H, int KV, int mpps,
-                        int num_pages, int max_chunks, float scale_log2, int window, int* __restrict__ err) {
+                        int num_pages, int max_chunks, float scale_log2, int window, int* __restrict__ err,
+                        float cap_raw) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     DecodeSmem& sm = *reinterpret_cast<DecodeSmem*>(smem_raw);
     float* comb = reinterpret_cast<float*>(smem_raw + sizeof(DecodeSmem));
@@ -200,6 +202,13 @@ attention_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_p
                     mma_bf16(s[t], qa[g].z, qb[g].z, qa[g].w, qb[g].w, kf[t][g].z, kf[t][g].w);
                 }
             }
+        }
+        if (cap_raw > 0.0f) {                  // a soft cap on the scores (in unscaled units), before the mask
+            const float inv_cap = 1.0f / cap_raw;
+#pragma unroll
+            for (int t = 0; t < 4; t++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) s[t][e] = ri_softcap(s[t][e], cap_raw, inv_cap);
         }
         // ---- mask, softmax over this warp's 32 keys (rows quad and quad+8) ---------------------------
         float mx[2] = {-FLT_MAX, -FLT_MAX};
@@ -385,6 +394,7 @@ struct StreamArgs {
     const int* seq_len;
     int seqs, KV, mpps, num_pages, window, max_pages, parts;
     int* err;
+    float cap_raw;          // a soft cap on the scores in unscaled units (cap / scale), 0 for none
 };
 
 __device__ __forceinline__ int warp_sum_int(int v) { return __reduce_add_sync(0xffffffffu, v); }
@@ -710,6 +720,13 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
             }
         }
         release_tile();
+        if (a.cap_raw > 0.0f) {                // a soft cap on the scores (in unscaled units), before the mask
+            const float inv_cap = 1.0f / a.cap_raw;
+#pragma unroll
+            for (int t = 0; t < 4; t++)
+#pragma unroll
+                for (int e = 0; e < 4; e++) s[t][e] = ri_softcap(s[t][e], a.cap_raw, inv_cap);
+        }
         // ---- mask (only the pages at the ends of the visible range need it), maximum, weights ---------------
         if (key0 < cc.first_key || rows < AD_PAGE) {
 #pragma unroll
@@ -1069,12 +1086,15 @@ extern "C" int ri_attention_decode_parts(int max_chunks) {
 // q, out [seqs, H, Dh] bf16; o_part [seqs, H, parts, Dh] f32; ml_part [seqs, H, parts, 2] f32 with
 // parts = ri_attention_decode_parts(max_chunks).  max_chunks * 128 must cover the longest sequence of the step.
 // sink [H] float32 or null: a learned term per head that joins the softmax's denominator only (the merge adds it).
-extern "C" int ri_attention_decode_sink(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,
-                                        float* ml_part, const int* page_table, const int* seq_slot, const int* seq_len,
-                                        int seqs, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
-                                        int max_chunks, float scale, int window, const float* sink, int* err_flag,
-                                        cudaStream_t stream) {
+// softcap > 0: score <- softcap * tanh(score / softcap) after the scale (0: none; the scale must then be positive).
+extern "C" int ri_attention_decode_cap(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,
+                                       float* ml_part, const int* page_table, const int* seq_slot, const int* seq_len,
+                                       int seqs, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
+                                       int max_chunks, float scale, int window, const float* sink, float softcap,
+                                       int* err_flag, cudaStream_t stream) {
     if (seqs == 0) return 0;
+    RI_REQUIRE(softcap >= 0.0f && (softcap == 0.0f || scale > 0.0f), "attention_decode: a soft cap %g with scale %g", (double)softcap, (double)scale);
+    const float cap_raw = softcap > 0.0f ? softcap / scale : 0.0f;
     RI_REQUIRE(Dh == AD_DH, "attention_decode: built for head_dim %d, called with %d", AD_DH, Dh);
     RI_REQUIRE(page_size == AD_PAGE, "attention_decode: pages of %d tokens, this kernel needs %d", page_size, AD_PAGE);
     RI_REQUIRE(H > 0 && KV > 0 && H % KV == 0, "attention_decode: %d heads over %d kv heads", H, KV);
@@ -1109,6 +1129,7 @@ extern "C" int ri_attention_decode_sink(const void* q, const void* k_pool, const
         a.parts = ADS_PARTS(max_chunks);
         a.window = window;
         a.err = err_flag;
+        a.cap_raw = cap_raw;
         // the most runs of ADS_MIN_PAGES pages that the step can have: fewer blocks than SMs, or fewer warps per
         // block (each with a deeper ring), when they do not fill the grid
         const long long runs = ((long long)seqs * KV * max_pages + ADS_MIN_PAGES - 1) / ADS_MIN_PAGES;
@@ -1140,7 +1161,7 @@ extern "C" int ri_attention_decode_sink(const void* q, const void* k_pool, const
     dim3 grid(max_chunks, KV, seqs);
     ri_launch_pdl(attention_decode_kernel, grid, dim3(32 * AD_WARPS), smem, stream,
                   (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, o_part, ml_part, page_table, seq_slot, seq_len,
-                  H, KV, mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
+                  H, KV, mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag, cap_raw);
     RI_CHECK_LAUNCH("attention_decode");
     MergeCut chunks_of_128;
     chunks_of_128.workers = 0;
@@ -1151,6 +1172,15 @@ extern "C" int ri_attention_decode_sink(const void* q, const void* k_pool, const
                   (const float*)o_part, (const float*)ml_part, (bf16*)out, seq_len, H, max_chunks, window, chunks_of_128, sink, err_flag);
     RI_CHECK_LAUNCH("attention_decode_merge");
     return 0;
+}
+
+extern "C" int ri_attention_decode_sink(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,
+                                        float* ml_part, const int* page_table, const int* seq_slot, const int* seq_len,
+                                        int seqs, int H, int KV, int Dh, int mpps, int page_size, int num_pages,
+                                        int max_chunks, float scale, int window, const float* sink, int* err_flag,
+                                        cudaStream_t stream) {
+    return ri_attention_decode_cap(q, k_pool, v_pool, out, o_part, ml_part, page_table, seq_slot, seq_len, seqs, H, KV, Dh,
+                                   mpps, page_size, num_pages, max_chunks, scale, window, sink, 0.0f, err_flag, stream);
 }
 
 extern "C" int ri_attention_decode(const void* q, const void* k_pool, const void* v_pool, void* out, float* o_part,

@@ -69,7 +69,7 @@ extern "C" int ri_attention_decode_noalloc(const void* q, const void* k_pool, co
     const int G = H / KV;
     attention_decode_kernel<<<grid, 32 * AD_WARPS, decode_smem_bytes(G < AD_ROWS ? G : AD_ROWS), stream>>>(
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, o_part, ml_part, page_table, seq_slot, seq_len, H, KV,
-        mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag);
+        mpps, num_pages, max_chunks, scale * 1.4426950408889634f, window, err_flag, 0.0f);
     RI_CHECK_LAUNCH("attention_decode_noalloc");
     MergeCut chunks_of_128;                    // the partial results are those of chunks of 128 keys
     chunks_of_128.workers = 0;

@@ -16,6 +16,7 @@
 // Formula: thanhauco/rust-inference src/attention.rs:4-8, 111-150.
 #include "common.cuh"
 #include "mma_helpers.cuh"
+#include "softcap.cuh"
 #include <float.h>
 #include <stddef.h>
 
@@ -68,7 +69,8 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
                          bf16* __restrict__ out, const int* __restrict__ page_table, const int* __restrict__ seq_slot,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int mpps,
                          int num_pages, float scale_log2, int window, const float* __restrict__ sink, int shared_kv,
-                         int v_dims, int* __restrict__ err) {
+                         int v_dims, int* __restrict__ err, float cap_raw) {
+    // cap_raw > 0: a soft cap on the scores in unscaled units (cap / scale), applied before the scale and the mask.
     // shared_kv: the values are the keys (one pool given as both): the key tiles serve as value tiles, nothing is
     // loaded twice and the block needs a third less shared memory.  v_dims: the leading value elements that are
     // wanted (a multiple of 16; the rest of an output row is written as zeros).
@@ -138,11 +140,12 @@ attention_prefill_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
         const int k0 = kb * PF_BN;
         const bool edge = (k0 + PF_BN - 1 > pos_first) || (window != 0 && k0 < ri_first_visible(pos_last, window));
         float mx[2] = {m[0], m[1]};
+        const float inv_cap = cap_raw > 0.0f ? 1.0f / cap_raw : 0.0f;
 #pragma unroll
         for (int t = 0; t < PF_BN / 8; t++)
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                float val = s[t][e] * scale_log2;
+                float val = (cap_raw > 0.0f ? ri_softcap(s[t][e], cap_raw, inv_cap) : s[t][e]) * scale_log2;
                 if (edge) {
                     int key = k0 + t * 8 + qc * 2 + (e & 1);
                     int p = my_pos[e >> 1];
@@ -219,12 +222,14 @@ extern "C" int ri_attention_prefill_head_dim() { return PF_DH; }
 
 // q, out [tokens, H, Dh] bf16; max_new = the most tokens one sequence brings in this step;
 // sink [H] float32 or null: a learned term per head that joins the softmax's denominator only
+// softcap > 0: score <- softcap * tanh(score / softcap) after the scale (0: none; the scale must then be positive)
 extern "C" int ri_attention_prefill(const void* q, const void* k_pool, const void* v_pool, void* out,
                                     const int* page_table, const int* seq_slot, const int* seq_start,
                                     const int* seq_len, int seqs, int max_new, int H, int KV, int Dh, int mpps,
                                     int page_size, int num_pages, float scale, int window, const float* sink,
-                                    int v_dims, int* err_flag, cudaStream_t stream) {
+                                    int v_dims, float softcap, int* err_flag, cudaStream_t stream) {
     if (seqs == 0 || max_new == 0) return 0;
+    RI_REQUIRE(softcap >= 0.0f && (softcap == 0.0f || scale > 0.0f), "attention_prefill: a soft cap %g with scale %g", (double)softcap, (double)scale);
     RI_REQUIRE(Dh == PF_DH, "attention_prefill: built for head_dim %d, called with %d", PF_DH, Dh);
     RI_REQUIRE(page_size == PF_PAGE, "attention_prefill: pages of %d tokens, this kernel needs %d", page_size, PF_PAGE);
     RI_REQUIRE(H > 0 && KV > 0 && H % KV == 0, "attention_prefill: %d heads over %d kv heads", H, KV);
@@ -245,7 +250,8 @@ extern "C" int ri_attention_prefill(const void* q, const void* k_pool, const voi
     dim3 grid((max_new + PF_BM - 1) / PF_BM, H, seqs);
     attention_prefill_kernel<<<grid, 32 * PF_WARPS, smem, stream>>>(
         (const bf16*)q, (const bf16*)k_pool, (const bf16*)v_pool, (bf16*)out, page_table, seq_slot, seq_start, seq_len,
-        H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, sink, shared_kv, v_dims, err_flag);
+        H, KV, mpps, num_pages, scale * 1.4426950408889634f, window, sink, shared_kv, v_dims, err_flag,
+        softcap > 0.0f ? softcap / scale : 0.0f);
     RI_CHECK_LAUNCH("attention_prefill");
     return 0;
 }

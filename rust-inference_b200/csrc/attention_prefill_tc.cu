@@ -57,6 +57,7 @@
 // Formula: thanhauco/rust-inference src/attention.rs:4-8, 111-150.
 #include "common.cuh"
 #include "mma_helpers.cuh"
+#include "softcap.cuh"
 #include <cuda.h>
 #include <float.h>
 
@@ -286,6 +287,7 @@ struct TcWork {
     const int* seq_len;
     int seqs, H, KV, mpps, groups_max, n_items, window;
     const float* sink;          // [H] or null: exp(sink[h]) joins head h's softmax denominator, with no key and no value
+    float cap_raw;              // a soft cap on the scores in unscaled units (cap / scale), 0 for none
 };
 // The items in the order (group of rows: late ones, which see the most keys, first; sequence; head).  Block c of G
 // takes item k G + c in its round k when k is even and item k G + G - 1 - c when k is odd, so the block that drew
@@ -569,6 +571,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(&tail.s_read[t][idx & 1])) : "memory");
+                if (work.cap_raw > 0.0f) {                            // a soft cap on the scores, before the mask
+                    const float inv_cap = 1.0f / work.cap_raw;
+#pragma unroll
+                    for (int i = 0; i < TC_BN; i++) s[i] = ri_softcap(s[i], work.cap_raw, inv_cap);
+                }
                 // a block of keys needs the mask if some query of this tile does not see all of it
                 const bool edge = (kb * TC_BN + TC_BN - 1 > tile_first) || (window != 0 && kb * TC_BN < ri_first_visible(tile_last, window));
                 if (edge) {
@@ -780,8 +787,10 @@ extern "C" int ri_attention_prefill_tc(const void* q, const void* k_pool, const 
                                        const int* page_table, const int* seq_slot, const int* seq_start,
                                        const int* seq_len, int tokens, int seqs, int max_new, int H, int KV, int Dh, int mpps,
                                        int page_size, int num_pages, float scale, int window, const float* sink,
-                                       int* err_flag, cudaStream_t stream) {
+                                       float softcap, int* err_flag, cudaStream_t stream) {
+    // softcap > 0: score <- softcap * tanh(score / softcap) after the scale (0: none)
     if (seqs == 0 || max_new == 0 || tokens == 0) return 0;
+    RI_REQUIRE(softcap >= 0.0f, "attention_prefill_tc: a soft cap is positive (0: none), got %g", (double)softcap);
     RI_REQUIRE(Dh == TC_DH, "attention_prefill_tc: built for head_dim %d, called with %d", TC_DH, Dh);
     RI_REQUIRE(page_size == TC_PAGE, "attention_prefill_tc: pages of %d tokens, this kernel needs %d", page_size, TC_PAGE);
     RI_REQUIRE(H > 0 && KV > 0 && H % KV == 0, "attention_prefill_tc: %d heads over %d kv heads", H, KV);
@@ -824,6 +833,7 @@ extern "C" int ri_attention_prefill_tc(const void* q, const void* k_pool, const 
     work.n_items = (int)n_items;
     work.window = window;
     work.sink = sink;
+    work.cap_raw = softcap > 0.0f ? softcap / scale : 0.0f;
     // one block per SM (the kernel's shared memory allows no second), each taking its items one after the other
     const int blocks = n_items < sms ? (int)n_items : sms;
     attention_prefill_tc_kernel<<<blocks, TC_THREADS, TC_SMEM_BYTES, stream>>>(

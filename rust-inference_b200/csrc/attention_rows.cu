@@ -6,6 +6,7 @@
 // sees are walked in strips (32 consecutive keys of one page, at fixed places of the sequence), and
 // for every strip
 //     score_j = (sum over d ascending of q[d] k_j[d], one accumulator) * scale       lane j = key j of the strip
+//     (with a soft cap c > 0: score_j <- c tanh(score_j / c))
 //     m' = max(m, max_j score_j);  c = exp(m - m');  p_j = exp(score_j - m')
 //     l = l c + (sum of the p_j over the warp's shuffle tree);  acc[d] = acc[d] c, then += p_j v_j[d] for j ascending
 // with exp the full-precision function, as thanhauco/rust-inference's CPU attention does a page at a
@@ -58,7 +59,7 @@ __host__ __device__ inline int ar_key_pitch(int Dh, bool vec4) { return vec4 ? D
 template <bool VEC4, int R>
 __device__ __forceinline__ void ar_strip(const float* __restrict__ qs, float* __restrict__ accs, float* __restrict__ ms,
                                          float* __restrict__ ls, const float* __restrict__ ks, const float* __restrict__ vs,
-                                         int row, int Dh, int kpitch, int j_lo, int j_hi, float scale, int lane) {
+                                         int row, int Dh, int kpitch, int j_lo, int j_hi, float scale, float softcap, int lane) {
     const bool mine = lane >= j_lo && lane <= j_hi;
     float s[R];
 #pragma unroll
@@ -90,6 +91,10 @@ __device__ __forceinline__ void ar_strip(const float* __restrict__ qs, float* __
         }
 #pragma unroll
         for (int r = 0; r < R; r++) s[r] = dot[r] * scale;
+        if (softcap > 0.0f) {
+#pragma unroll
+            for (int r = 0; r < R; r++) s[r] = softcap * tanhf(s[r] / softcap);
+        }
     }
     float corr[R], p[R];
 #pragma unroll
@@ -146,7 +151,7 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, con
                       T* __restrict__ out, const int* __restrict__ page_table, const int* __restrict__ seq_slot,
                       const int* __restrict__ seq_start, const int* __restrict__ seq_len, int H, int KV, int Dh,
                       int mpps, int page_size, int num_pages, int tile_q, int group_chunk, float scale, int window,
-                      const float* __restrict__ sink, int* __restrict__ err) {
+                      const float* __restrict__ sink, float softcap, int* __restrict__ err) {
     extern __shared__ __align__(16) float ar_smem[];
     const int b = blockIdx.z;
     const int t_begin = seq_start[b], n_new = seq_start[b + 1] - t_begin;
@@ -222,9 +227,9 @@ attention_rows_kernel(const T* __restrict__ q, const T* __restrict__ k_pool, con
             if (j_lo > j_hi) continue;                                // none: the rows' state stays as it is
             const int row_a = i * ng + g_first;
             if (g_first + 1 < ng)
-                ar_strip<VEC4, 2>(qs, accs, ms, ls, ks, vs, row_a, Dh, kpitch, j_lo, j_hi, scale, lane);
+                ar_strip<VEC4, 2>(qs, accs, ms, ls, ks, vs, row_a, Dh, kpitch, j_lo, j_hi, scale, softcap, lane);
             else
-                ar_strip<VEC4, 1>(qs, accs, ms, ls, ks, vs, row_a, Dh, kpitch, j_lo, j_hi, scale, lane);
+                ar_strip<VEC4, 1>(qs, accs, ms, ls, ks, vs, row_a, Dh, kpitch, j_lo, j_hi, scale, softcap, lane);
         }
         key0 += width;
     }
@@ -259,7 +264,7 @@ template <typename T, bool VEC4>
 static int ar_launch(const void* q, const void* k_pool, const void* v_pool, void* out, const int* page_table,
                      const int* seq_slot, const int* seq_start, const int* seq_len, int seqs, int max_new, int H, int KV,
                      int Dh, int mpps, int page_size, int num_pages, float scale, int window, const float* sink,
-                     int* err_flag, cudaStream_t stream) {
+                     float softcap, int* err_flag, cudaStream_t stream) {
     int tile_q, group_chunk;
     size_t smem;
     const int G = H / KV;
@@ -276,17 +281,18 @@ static int ar_launch(const void* q, const void* k_pool, const void* v_pool, void
     dim3 grid((max_new + tile_q - 1) / tile_q, (unsigned)gy, seqs);
     attention_rows_kernel<T, VEC4><<<grid, 32 * AR_WARPS, smem, stream>>>(
         (const T*)q, (const T*)k_pool, (const T*)v_pool, (T*)out, page_table, seq_slot, seq_start, seq_len, H, KV, Dh, mpps,
-        page_size, num_pages, tile_q, group_chunk, scale, window, sink, err_flag);
+        page_size, num_pages, tile_q, group_chunk, scale, window, sink, softcap, err_flag);
     RI_CHECK_LAUNCH("attention_rows");
     return 0;
 }
 
 // q, out [tokens, H, Dh]; max_new = the most tokens one sequence brings in this step
 // sink [H] float32 or null: a learned term per head that joins the softmax's denominator only
+// softcap > 0: score <- softcap * tanh(score / softcap) after the scale (0: none)
 extern "C" int ri_attention_rows(const void* q, const void* k_pool, const void* v_pool, void* out, const int* page_table,
                                  const int* seq_slot, const int* seq_start, const int* seq_len, int seqs, int max_new,
                                  int H, int KV, int Dh, int mpps, int page_size, int num_pages, float scale, int window,
-                                 const float* sink, int dtype, int* err_flag, cudaStream_t stream) {
+                                 const float* sink, float softcap, int dtype, int* err_flag, cudaStream_t stream) {
     if (seqs == 0 || max_new == 0) return 0;
     RI_REQUIRE(seqs > 0 && max_new > 0 && H > 0 && KV > 0 && Dh > 0 && page_size > 0 && mpps > 0, "attention_rows: bad sizes");
     RI_REQUIRE(H % KV == 0, "attention_rows: %d heads are not a multiple of %d kv heads", H, KV);
@@ -297,7 +303,7 @@ extern "C" int ri_attention_rows(const void* q, const void* k_pool, const void* 
     const uintptr_t align = f32 ? 15 : 7;
     const bool vec4 = Dh % 4 == 0 && (((uintptr_t)q | (uintptr_t)k_pool | (uintptr_t)v_pool) & align) == 0;
 #define AR_GO(T, V) ar_launch<T, V>(q, k_pool, v_pool, out, page_table, seq_slot, seq_start, seq_len, seqs, max_new, H, KV, \
-                                    Dh, mpps, page_size, num_pages, scale, window, sink, err_flag, stream)
+                                    Dh, mpps, page_size, num_pages, scale, window, sink, softcap, err_flag, stream)
     if (f32) return vec4 ? AR_GO(float, true) : AR_GO(float, false);
     return vec4 ? AR_GO(__nv_bfloat16, true) : AR_GO(__nv_bfloat16, false);
 #undef AR_GO

@@ -34,19 +34,21 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "attention_rows": ("attention_rows.cu", "common.cuh"),
     "linear_f32": ("linear_f32.cu", "common.cuh"),
     "streams": ("streams.cu", "common.cuh"),
+    "norm_gains": ("norm_gains.cu", "common.cuh"),
+    "qkv_prep": ("qkv_prep.cu", "common.cuh"),
     "latent_attention": ("latent_attention.cu", "common.cuh"),
     "gla": ("gla.cu", "common.cuh"),
     "pair_embedding": ("pair_embedding.cu", "common.cuh"),
     "delta_rule": ("delta_rule.cu", "common.cuh"),
     "moe": ("moe.cu", "common.cuh", "mma_helpers.cuh"),
     "sampling": ("sampling.cu", "common.cuh"),
-    "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh"),
-    "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh"),
+    "attention_decode": ("attention_decode.cu", "common.cuh", "mma_helpers.cuh", "softcap.cuh"),
+    "attention_prefill": ("attention_prefill.cu", "common.cuh", "mma_helpers.cuh", "softcap.cuh"),
     "linear_skinny": ("linear_skinny.cu", "common.cuh", "mma_helpers.cuh", "linear_skinny_geometry.cuh"),
     "linear_stream_tc": ("linear_stream_tc.cu", "common.cuh", "mma_helpers.cuh"),
-    "attention_prefill_tc": ("attention_prefill_tc.cu", "common.cuh", "mma_helpers.cuh"),
+    "attention_prefill_tc": ("attention_prefill_tc.cu", "common.cuh", "mma_helpers.cuh", "softcap.cuh"),
     "attention_decode_noalloc": ("attention_decode_noalloc.cu", "attention_decode_noalloc.h", "attention_decode.cu",
-                                 "common.cuh", "mma_helpers.cuh"),
+                                 "common.cuh", "mma_helpers.cuh", "softcap.cuh"),
     "random_fill": ("random_fill.cu", "common.cuh", "random_fill.cuh"),
     # host code only: the same random values as random_fill.cu gives on the device
     "host_random": ("host_random.cpp", "random_fill.cuh"),

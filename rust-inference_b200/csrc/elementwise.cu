@@ -610,3 +610,20 @@ extern "C" int ri_scale_f32(float* x, long long total, float factor, cudaStream_
     RI_CHECK_LAUNCH("scale_f32");
     return 0;
 }
+
+// ---------------------------------------------------------------------------
+// x <- cap * tanh(x / cap), in place, float32 (logits with a soft cap).
+__global__ void softcap_f32_kernel(float* __restrict__ x, size_t total, float cap) {
+    pdl_trigger();
+    pdl_wait();
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+
+extern "C" int ri_softcap_f32(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    RI_REQUIRE(cap > 0.0f, "softcap: the cap must be positive, got %g", (double)cap);
+    ri_launch_pdl(softcap_f32_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, (size_t)total, cap);
+    RI_CHECK_LAUNCH("softcap_f32");
+    return 0;
+}

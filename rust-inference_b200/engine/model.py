@@ -51,6 +51,9 @@ def _part_tensors(spec):
         for part, family, record in part_class("block", layer).slots(layer):
             for local, info in part_class(family, record).param_infos(record).items():
                 yield layer.prefix(part) + local, info, ("layer", i, part), local
+    if spec.pass_entry is not None:
+        for local, info in part_class("link", spec.pass_entry).param_infos(spec.pass_entry).items():
+            yield local, info, ("pass_entry",), local
     head = spec.head_record()
     for local, info in part_class("head", head).param_infos(head).items():
         if local == "weight" and spec.tie_embeddings:
@@ -71,6 +74,13 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, self.env)
         self.embed_part = build_part("embedding", spec.embedding_record(), self.env)
         self.head_part = build_part("head", spec.head_record(), self.env)
+        # what a pass over a repeated run of layers adds on entry (the schedule says where)
+        self.pass_entry = None
+        if spec.pass_entry is not None:
+            self.pass_entry = build_part("link", spec.pass_entry, self.env)
+            self.pass_entry.bind(self.embed_part)
+        elif any(e.enters >= 0 for e in spec.schedule):
+            raise ValueError("the schedule enters passes, but the model has no pass_entry record")
         self.config = None
         self.cache_entry_layers = spec.cache_entries()
         # an embedding that keeps state per sequence has a cache entry of its own, after the layers' entries
@@ -117,6 +127,8 @@ class Model:
                 self.embed_part.load(tensors)
             elif owner == ("final_norm",):
                 self.final_norm.load(tensors)
+            elif owner == ("pass_entry",):
+                self.pass_entry.load(tensors)
             elif owner == ("head",):
                 if "weight" not in tensors:
                     tensors["weight"] = self.embed_part.table          # tied: the same storage
@@ -169,6 +181,7 @@ class Model:
     def graph_safe(self) -> bool:
         """Whether one-token steps of this model may be replayed from a CUDA graph."""
         parts = [p for b in self.blocks for _, p, _, _ in b.parts()] + [self.final_norm, self.embed_part, self.head_part]
+        parts += [self.pass_entry] if self.pass_entry is not None else []
         parts += [b.mixer.position for b in self.blocks if hasattr(b.mixer, "position")]
         return all(getattr(p, "graph_safe", False) for p in parts)
 
@@ -181,6 +194,7 @@ class Model:
         embedding only counts when asked, a step reads a few rows of it)."""
         n = sum(p.weight_bytes() for b in self.blocks for _, p, _, _ in b.parts())
         n += self.final_norm.weight_bytes() + self.head_part.weight_bytes()
+        n += self.pass_entry.weight_bytes() if self.pass_entry is not None else 0
         if with_embedding and self.head is not self.embedding:
             n += self.embed_part.weight_bytes()
         return n
@@ -195,6 +209,8 @@ class Model:
                 resid = self.embed_part(ids, ctx)
         delta = None
         for e in self.spec.schedule:
+            if e.enters >= 0:
+                delta = self.pass_entry(delta, e.enters, ids)
             resid, delta = self.blocks[e.layer](resid, delta, ctx, cache.layer(e.cache, e.writes))
         if self.final_norm.takes_hint:
             x = self.final_norm(resid, delta, want_rows, self.head_part.reads_first())

@@ -46,19 +46,23 @@ _SIGNATURES = {
     ("elementwise", "ri_add_rows"): [_P, _P, _L, _I, _P],
     ("elementwise", "ri_silu_mul"): [_P, _P, _I, _I, _I, _I, _P],
     ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
-    ("attention_rows", "ri_attention_rows"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _P, _P],
+    ("attention_rows", "ri_attention_rows"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _F, _I, _P, _P],
+    ("elementwise", "ri_softcap_f32"): [_P, _L, _F, _P],
+    ("norm_gains", "ri_norm_gains"): [_P] * 6 + [_P, _I, _F] + [_P] * 6 + [_I, _I, _F, _I, _P, _P],
+    ("qkv_prep", "ri_qkv_prep"): [_P, _L, _I, _I, _I] + [_P] * 9 + [_I, _I, _I, _I, _F] + [_I] * 10 + [_P, _P],
     ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
     ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _P, _I, _P],
     ("sampling", "ri_sample_work_bytes"): [_I, _I],
     ("sampling", "ri_argmax"): [_P, _L, _I, _I, _P, _P, _P, _P],
     ("sampling", "ri_mark_seen"): [_P, _L, _P, _P, _I, _I, _P],
     ("attention_decode", "ri_attention_decode_sink"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _P, _P],
+    ("attention_decode", "ri_attention_decode_cap"): [_P] * 9 + [_I] * 8 + [_F, _I, _P, _F, _P, _P],
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny_act"): [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny_gated"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
-    ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _P, _P],
-    ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _P, _P],
+    ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _F, _P, _P],
+    ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _F, _P, _P],
 }
 DECODE_CHUNK = 128          # keys per partial result of the decode attention kernel
 MAX_FAST_HEAD_DIM = 256
@@ -647,12 +651,116 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
     return q
 
 
+def rms_gains(resid: torch.Tensor, gains, eps: float, out_dtype: torch.dtype, terms=(), entry=None,
+              rows: Optional[torch.Tensor] = None, then: Optional[torch.Tensor] = None):
+    """RMS norm of the float32 residual ``resid`` [n, dim] with one or two gains: a tuple of x / sqrt(mean(x^2) + eps) * g
+    for every g of ``gains``, from one pass.  First whatever joins the residual, in float32: ``terms``, up to two pending
+    outputs as pairs (tensor [n, dim] of the compute dtype, a float32 factor [1] or None for 1), two of them summed
+    before they are added (x + (a + b)); then ``entry`` (an object with ``ids``, ``table``, ``scale``, ``vec``):
+    table[ids] * scale (``ids`` None: not) and the vector ``vec`` [dim].  The new residual is written back unless ``rows``
+    (int32 indices: only those rows are read, in that order) is given.  ``then``: unused (a hint)."""
+    _need(resid, "resid", torch.float32)
+    n, dim = resid.shape
+    gains = tuple(gains)
+    if not 1 <= len(gains) <= 2:
+        raise KernelError(f"rms_gains: {len(gains)} gains (one or two)")
+    for g in gains:
+        _need(g, "gain", torch.float32, (dim,))
+    terms = list(terms)
+    if len(terms) > 2:
+        raise KernelError("rms_gains: at most two pending outputs")
+    for y, w in terms:
+        _need(y, "pending output", out_dtype, (n, dim))
+        if w is not None:
+            _need(w, "factor of a pending output", torch.float32, (1,))
+    terms += [(None, None)] * (2 - len(terms))
+    ids = table = vec = None
+    scale, vocab = 1.0, 0
+    if entry is not None:
+        ids, table, scale, vec = entry.ids, entry.table, float(entry.scale), entry.vec
+        if ids is not None:
+            _need(ids, "ids", torch.int32, (n,))
+            _need(table, "table", out_dtype)
+            if table.dim() != 2 or table.shape[1] != dim:
+                raise KernelError(f"rms_gains: table {tuple(table.shape)} does not fit rows of {dim}")
+            vocab = table.shape[0]
+        if vec is not None:
+            _need(vec, "vec", torch.float32, (dim,))
+        if rows is not None and (ids is not None or vec is not None):
+            raise KernelError("rms_gains: the terms of an entry join whole steps, not selected rows")
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+    n_out = n if rows is None else rows.numel()
+    outs = tuple(torch.empty((n_out, dim), dtype=out_dtype, device=resid.device) for _ in gains)
+    _call("norm_gains", "ri_norm_gains", resid.data_ptr(), _ptr(terms[0][0]), _ptr(terms[0][1]), _ptr(terms[1][0]),
+          _ptr(terms[1][1]), _ptr(ids), _ptr(table), int(vocab), scale, _ptr(vec), _ptr(rows), gains[0].data_ptr(),
+          gains[1].data_ptr() if len(gains) > 1 else None, outs[0].data_ptr(), outs[1].data_ptr() if len(gains) > 1 else None,
+          n_out, dim, float(eps), _code(out_dtype), error_flag(resid.device).data_ptr(), _stream())
+    return outs
+
+
+def qkv_prep(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, heads: int, kv_heads: int, Dp: int, Dk: int,
+             bias: Optional[torch.Tensor], rope_table: Optional[torch.Tensor], rot: int, pairs: bool, unit: bool,
+             eps: float, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], page_table: torch.Tensor,
+             tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
+    """Between the q/k/v product and the attention kernels: ``proj`` [tokens, N] holds the q heads from column ``q_col``,
+    the k heads from ``k_col`` and the v heads from ``v_col`` (< 0: none, the values are the keys as cached), every head
+    ``Dp`` columns wide with ``Dk`` true elements.  ``bias`` (float32, by column of the product) is added first; the first
+    ``rot`` elements of q and k heads are turned by ``rope_table`` [positions, rot/2, 2] (``pairs``: partners are
+    neighbours, else half a rotated part apart); with ``unit`` q and k heads are then divided by their root mean square
+    over ``Dk`` (eps inside the root, no gain).  k (and v) go to the token's place in the pools
+    [pages, KV, page_size, Dp]; returns q [tokens, H, Dp].  All of it in float32."""
+    _need(proj, "proj")
+    tokens, ld = proj.shape
+    nv = 0 if v_col < 0 else kv_heads
+    if q_col + heads * Dp > ld or k_col + kv_heads * Dp > ld or (nv and v_col + nv * Dp > ld):
+        raise KernelError("qkv_prep: the projection is narrower than its columns")
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() < max(q_col + heads * Dp, k_col + kv_heads * Dp, v_col + nv * Dp):
+            raise KernelError("qkv_prep: the bias vector is shorter than the columns it is indexed by")
+    rope_rows = 0
+    if rope_table is not None:
+        _need(rope_table, "rope_table", torch.float32)
+        if rope_table.dim() != 3 or rope_table.shape[1] != rot // 2 or rope_table.shape[2] != 2:
+            raise KernelError(f"rope table must be [positions, {rot // 2}, 2], got {tuple(rope_table.shape)}")
+        rope_rows = rope_table.shape[0]
+    if write_kv:
+        if k_pool is None:
+            raise KernelError("qkv_prep: appending needs the cache pools")
+        _need(k_pool, "k_pool", proj.dtype)
+        pages, kvh, page_size, dp = k_pool.shape
+        if (kvh, dp) != (kv_heads, Dp):
+            raise KernelError(f"qkv_prep: pool {tuple(k_pool.shape)} does not fit {kv_heads} kv heads of {Dp}")
+        if nv:
+            _need(v_pool, "v_pool", proj.dtype, k_pool.shape)
+    else:
+        pages, page_size = 1, 1
+    _need(page_table, "page_table", torch.int32)
+    for t, n in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (seq_slot, "seq_slot")):
+        _need(t, n, torch.int32)
+    q = torch.empty((tokens, heads, Dp), dtype=proj.dtype, device=proj.device)
+    _call("qkv_prep", "ri_qkv_prep", proj.data_ptr(), ld, int(q_col), int(k_col), int(v_col), _ptr(bias), q.data_ptr(),
+          _ptr(k_pool) if write_kv else None, _ptr(v_pool) if write_kv and nv else None, page_table.data_ptr(),
+          tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(), _ptr(rope_table), rope_rows, int(rot),
+          1 if pairs else 0, 1 if unit else 0, float(eps), tokens, heads, kv_heads, Dp, Dk, page_table.shape[1], page_size,
+          pages, 1 if write_kv else 0, _code(proj.dtype), error_flag(proj.device).data_ptr(), _stream())
+    return q
+
+
 def _mask(window: int, chunk: int) -> int:
     """The kernels' one mask integer: a window of the last ``window`` keys, or (negative) chunks of ``chunk``
     positions counted from the sequence's start, of which a query sees its own up to itself."""
     if window < 0 or chunk < 0 or (window and chunk):
         raise KernelError(f"attention: window {window} and chunk {chunk}: at most one of them, none negative")
     return int(window) if window else -int(chunk)
+
+
+def _cap(softcap: float) -> float:
+    softcap = float(softcap or 0.0)
+    if softcap < 0.0:
+        raise KernelError(f"a soft cap is positive (0: none), got {softcap}")
+    return softcap
 
 
 def _sink(sink: Optional[torch.Tensor], heads: int) -> Optional[int]:
@@ -664,12 +772,13 @@ def _sink(sink: Optional[torch.Tensor], heads: int) -> Optional[int]:
 
 def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
               seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int, scale: float,
-              window: int = 0, sink: Optional[torch.Tensor] = None, chunk: int = 0) -> torch.Tensor:
+              window: int = 0, sink: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """Causal attention of the step's new tokens (q [tokens, H, Dh], sequences back to back as
     ``seq_start`` says) over the paged cache, which already holds their keys and values: float32 or
     bfloat16, any head size up to 512, any page size.  Every (token, head) is computed in one fixed
     order that depends on its own position only, so the result does not depend on the step's cutting.
     ``sink`` [H] (float32): exp(sink[h]) joins head h's softmax denominator, with no key and no value.
+    ``softcap`` > 0: score <- softcap * tanh(score / softcap) after the scale.
     ``v_pool`` may be ``k_pool`` itself (values that are the keys: latent attention)."""
     _need(q, "q")
     tokens, H, Dh = q.shape
@@ -686,8 +795,8 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_
     out = torch.empty_like(q)
     _call("attention_rows", "ri_attention_rows", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(), out.data_ptr(),
           page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(), seqs, int(max_new),
-          H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), _mask(window, chunk), _sink(sink, H), _code(q.dtype),
-          error_flag(q.device).data_ptr(), _stream())
+          H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), _mask(window, chunk), _sink(sink, H), _cap(softcap),
+          _code(q.dtype), error_flag(q.device).data_ptr(), _stream())
     return out
 
 
@@ -704,7 +813,7 @@ def _decode_parts(head_dim: int, chunks: int) -> int:
 
 def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                      seq_slot: torch.Tensor, seq_len: torch.Tensor, scale: float, window: int,
-                     max_len: int, sink: Optional[torch.Tensor] = None, chunk: int = 0) -> torch.Tensor:
+                     max_len: int, sink: Optional[torch.Tensor] = None, chunk: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """Attention of one new token per sequence (q [seqs, H, Dh], bfloat16) over the
     paged cache, keys split into chunks of ``DECODE_CHUNK``; ``max_len`` bounds the
     sequences' lengths after this step and sizes the scratch memory."""
@@ -725,17 +834,18 @@ def attention_decode(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor
     o_part = torch.empty((seqs, H, parts, Dh), dtype=torch.float32, device=q.device)
     ml_part = torch.empty((seqs, H, parts, 2), dtype=torch.float32, device=q.device)
     out = torch.empty_like(q)
-    _call("attention_decode", "ri_attention_decode_sink", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
+    _call("attention_decode", "ri_attention_decode_cap", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), o_part.data_ptr(), ml_part.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(),
           seq_len.data_ptr(), seqs, H, KV, Dh, page_table.shape[1], page_size, pages, chunks, float(scale),
-          _mask(window, chunk), _sink(sink, H), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+          _mask(window, chunk), _sink(sink, H), _cap(softcap), error_flag(q.device).data_ptr(), _stream(),
+          defines={"RI_HEAD_DIM": Dh})
     return out
 
 
 def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, page_table: torch.Tensor,
                       seq_slot: torch.Tensor, seq_start: torch.Tensor, seq_len: torch.Tensor, max_new: int,
                       scale: float, window: int, sink: Optional[torch.Tensor] = None, v_dims: int = 0,
-                      chunk: int = 0) -> torch.Tensor:
+                      chunk: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """Attention of the step's new tokens (q [tokens, H, Dh], bfloat16, sequences back
     to back as ``seq_start`` says) over the paged cache, which already holds their keys
     and values; ``max_new`` is the most tokens one sequence brings.  ``v_pool`` may be ``k_pool``
@@ -761,12 +871,13 @@ def attention_prefill(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
         _call("attention_prefill_tc", "ri_attention_prefill_tc", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
               out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
               q.shape[0], seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale),
-              _mask(window, chunk), _sink(sink, H), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+              _mask(window, chunk), _sink(sink, H), _cap(softcap), error_flag(q.device).data_ptr(), _stream(),
+              defines={"RI_HEAD_DIM": Dh})
         return out
     _call("attention_prefill", "ri_attention_prefill", q.data_ptr(), k_pool.data_ptr(), v_pool.data_ptr(),
           out.data_ptr(), page_table.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seq_len.data_ptr(),
           seqs, int(max_new), H, KV, Dh, page_table.shape[1], page_size, pages, float(scale), _mask(window, chunk),
-          _sink(sink, H), int(v_dims), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
+          _sink(sink, H), int(v_dims), _cap(softcap), error_flag(q.device).data_ptr(), _stream(), defines={"RI_HEAD_DIM": Dh})
     return out
 
 
@@ -845,6 +956,14 @@ def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
     _need(x, "x", torch.float32)
     if factor != 1.0:
         _call("elementwise", "ri_scale_f32", x.data_ptr(), x.numel(), float(factor), _stream())
+    return x
+
+
+def softcap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32); ``cap`` 0: nothing."""
+    _need(x, "x", torch.float32)
+    if cap:
+        _call("elementwise", "ri_softcap_f32", x.data_ptr(), x.numel(), _cap(cap), _stream())
     return x
 
 

@@ -12,6 +12,15 @@ Values of another size than the keys (``v_head_dim``): the kernels work with one
 part runs them at Dp = the larger of the two rounded up to 16 and pads at load: the query, key and
 value matrices get zero rows (a zero query element times a zero key element adds exactly 0 to a
 score), the output matrix zero columns.  Nothing of the padding reaches a result.
+
+Further options of the record, each a field with its constants: biases on the q/k/v projections
+(added in float32 by the kernel that rotates and appends), values that are the keys as cached
+(no v tensor, one pool), queries and keys divided by their root mean square AFTER the rotation
+(no gain), a soft-cap on the scores, and a sigmoid gate per output element from a projection of
+the mixer's input, stacked into the q/k/v product.  A record that uses any of them runs the
+"extended" order of work: one product for q, k, (v), (gate); ``ops.qkv_prep`` (bias, rotation,
+unit norm, append); attention; gate; output projection.  Heads are then always padded to a
+multiple of 16 elements, so that the tensor-core kernels take every size.
 """
 from __future__ import annotations
 
@@ -47,6 +56,26 @@ class Attention(Mixer):
         self.rot = getattr(spec.position, "rot", None) or getattr(spec.position, "rotary_dim", 0)
         if self.rot > self.Dk:
             raise ValueError(f"{self.rot} rotated elements in heads of {self.Dk}")
+        self.bias_of = tuple(getattr(spec, "bias", ()) or ())
+        self.keys_are_values = getattr(spec, "values", "own") == "keys"
+        self.unit_rms = bool(getattr(spec, "unit_rms", False))
+        self.softcap = float(getattr(spec, "softcap", 0.0) or 0.0)
+        self.gated = getattr(spec, "gate", "") or ""
+        if getattr(spec, "values", "own") not in ("own", "keys"):
+            raise ValueError(f"values {spec.values!r}: 'own' or 'keys'")
+        if self.gated not in ("", "element"):
+            raise ValueError(f"gate {self.gated!r} is not built (known: element)")
+        if set(self.bias_of) - {"q", "k", "v"}:
+            raise ValueError(f"biases {self.bias_of}: of q, k, v")
+        self.extended = bool(self.bias_of or self.keys_are_values or self.unit_rms or self.softcap or self.gated)
+        if self.extended:
+            if spec.qk_norm is not None or spec.sink or spec.chunk:
+                raise ValueError("the extended attention options do not combine with a per-head norm before the "
+                                 "rotation, a sink or a chunked mask")
+            if self.keys_are_values and self.Dv != self.Dk:
+                raise ValueError(f"values that are the keys have the keys' size {self.Dk}, not {self.Dv}")
+            self.Dp = -(-max(self.Dk, self.Dv) // 16) * 16
+            self.bias = None
 
     @classmethod
     def param_infos(cls, spec):
@@ -54,6 +83,14 @@ class Attention(Mixer):
         Dv = spec.v_head_dim or Dh
         q, k, v, o, sink = spec.names
         infos = {q: ParamInfo((H * Dh, D)), k: ParamInfo((KV * Dh, D)), v: ParamInfo((KV * Dv, D)), o: ParamInfo((D, H * Dv))}
+        if getattr(spec, "values", "own") == "keys":
+            del infos[v]
+        suffix = getattr(spec, "bias_suffix", ".b")
+        for which, name in (("q", q), ("k", k), ("v", v)):
+            if which in (getattr(spec, "bias", ()) or ()) and name in infos:
+                infos[name + suffix] = ParamInfo(infos[name].shape[:1], "vector")
+        if getattr(spec, "gate", ""):
+            infos[spec.gate_name] = ParamInfo((H * Dv, D))
         if spec.qk_norm is not None:
             infos["q_norm.weight"] = ParamInfo((Dh,), "gain")
             infos["k_norm.weight"] = ParamInfo((Dh,), "gain")
@@ -73,8 +110,27 @@ class Attention(Mixer):
             out[:, :size] = t.view(heads, size, D)
             return out.view(heads * Dp, D)
 
-        self.qkv = torch.cat([rows(tensors[q], s.num_heads, self.Dk), rows(tensors[k], s.num_kv_heads, self.Dk),
-                              rows(tensors[v], s.num_kv_heads, self.Dv)], dim=0).contiguous()
+        blocks = [rows(tensors[q], s.num_heads, self.Dk), rows(tensors[k], s.num_kv_heads, self.Dk)]
+        if not self.keys_are_values:
+            blocks.append(rows(tensors[v], s.num_kv_heads, self.Dv))
+        if self.gated:
+            blocks.append(rows(tensors[s.gate_name], s.num_heads, self.Dv))
+        self.qkv = torch.cat(blocks, dim=0).contiguous()
+        if self.extended:
+            # the columns of the product: q heads, k heads, v heads (unless the keys serve), gate; the biases as one
+            # float32 vector over the q/k/v columns, zero where a projection has none and in the padding
+            H, KV = s.num_heads, s.num_kv_heads
+            self.k_col = H * Dp
+            self.v_col = -1 if self.keys_are_values else (H + KV) * Dp
+            self.g_col = (H + KV + (0 if self.keys_are_values else KV)) * Dp
+            self.bias = None
+            if self.bias_of:
+                bias = torch.zeros(self.g_col, dtype=torch.float32, device=self.qkv.device)
+                for which, name, col, heads, size in (("q", q, 0, H, self.Dk), ("k", k, self.k_col, KV, self.Dk),
+                                                      ("v", v, self.v_col, KV, self.Dv)):
+                    if which in self.bias_of and col >= 0:
+                        bias[col:col + heads * Dp].view(heads, Dp)[:, :size] = tensors[name + s.bias_suffix].float().view(heads, size)
+                self.bias = bias
         wo = tensors[o]
         if self.Dv != Dp:
             padded = wo.new_zeros((D, s.num_heads, Dp))
@@ -94,12 +150,46 @@ class Attention(Mixer):
 
     def cache_request(self):
         s = self.spec
-        return CacheRequest(kv_heads=s.num_kv_heads, head_dim=self.Dp, window=s.window, chunk=s.chunk)
+        return CacheRequest(kv_heads=s.num_kv_heads, head_dim=self.Dp, window=s.window, chunk=s.chunk,
+                            shared_kv=self.keys_are_values)
 
     def prepare(self, max_positions):
         self.position.prepare(max_positions)
 
+    def _extended(self, x, ctx, cache):
+        s = self.spec
+        T, H, KV, Dp = x.shape[0], s.num_heads, s.num_kv_heads, self.Dp
+        with section("attn q/k/v proj"):
+            proj = ops.linear(x, self.qkv)
+        table = self.position.fused_table()
+        if table is None and type(self.position).apply is not PositionEncoding.apply:
+            raise ValueError("the extended attention options need a position part whose table the kernel applies")
+        with section("attn norm/rope/append"):
+            q = ops.qkv_prep(proj, 0, self.k_col, self.v_col, H, KV, Dp, self.Dk, self.bias, table,
+                             self.rot if table is not None else 0, getattr(self.position, "pairs", False),
+                             self.unit_rms, s.unit_eps, cache.k_pool, cache.v_pool, cache.page_table, ctx.tok_seq,
+                             ctx.tok_pos, ctx.seq_slot, write_kv=cache.writes)
+        fast = ops.fast_attention_supported(q.dtype, Dp, cache.page_size)
+        with section("attention"):
+            if fast and ctx.decode_only:
+                out = ops.attention_decode(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot, ctx.seq_len,
+                                           self.scale, s.window, ctx.len_bucket, softcap=self.softcap)
+            elif fast:
+                out = ops.attention_prefill(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot,
+                                            ctx.seq_start, ctx.seq_len, ctx.max_new, self.scale, s.window,
+                                            softcap=self.softcap)
+            else:
+                out = ops.attention(q, cache.k_pool, cache.v_pool, cache.page_table, ctx.seq_slot, ctx.seq_start,
+                                    ctx.seq_len, ctx.max_new, self.scale, s.window, softcap=self.softcap)
+        if self.gated:
+            with section("attn gate"):
+                ops.gate_heads(out, proj[:, self.g_col:self.g_col + H * Dp], "sigmoid")
+        with section("attn o proj"):
+            return ops.linear(out.view(T, H * Dp), self.o)
+
     def __call__(self, x, ctx, cache):
+        if self.extended:
+            return self._extended(x, ctx, cache)
         s = self.spec
         with section("attn q/k/v proj"):
             qkv = ops.linear(x, self.qkv)

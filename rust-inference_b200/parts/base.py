@@ -109,10 +109,22 @@ class Pending:
     (``mix`` None: the identity; ``out`` None: ones).  ``more``: further outputs that join in the same pass (a layer
     whose mixer and feed-forward run side by side, a mixer that is a weighted sum of two), as pairs (tensor, weights
     [streams] or None for ones): x_t <- ... + out[t] y + w2[t] y2 + ..., the sum taken in float32."""
-    y: torch.Tensor
+    y: Optional[torch.Tensor]
     mix: Optional[torch.Tensor] = None
     out: Optional[torch.Tensor] = None
     more: tuple = ()
+    # float32 terms that join after the outputs (an :class:`Injection`); ``y`` may then be None (nothing pending)
+    entry: object = None
+
+
+@dataclass
+class Injection:
+    """Float32 terms that join the residual right before a layer, after whatever is pending: first the embedding's
+    rows once more, table[ids] * scale (``ids`` None: not), then the vector ``vec`` [hidden] on every token."""
+    ids: Optional[torch.Tensor]
+    table: Optional[torch.Tensor]
+    scale: float
+    vec: Optional[torch.Tensor]
 
 
 @dataclass

@@ -98,6 +98,27 @@ class ParallelBlock(BlockBase):
         return resid, self.link.pending(a, f)
 
 
+@register_block("parallel_norms")
+class ParallelNormsBlock(BlockBase):
+    """A mixer and a feed-forward (optional) side by side, each behind a gain of its own over the one RMS statistic of
+    the same residual: x <- x + (mixer(x r g1) + ffn(x r g2)).  One norm part (``rms_gains``) gives both inputs from one
+    pass; the outputs join the residual together through the layer's connection, in float32, in the next norm."""
+
+    @classmethod
+    def slots(cls, spec):
+        out = [("norms", "norm", spec.norms), ("link", "link", spec.link), ("mixer", "mixer", spec.mixer)]
+        if spec.ffn is not None:
+            out.append(("ffn", "ffn", spec.ffn))
+        return tuple(out)
+
+    def __call__(self, resid, delta, ctx, cache):
+        xs = self.norms(resid, delta, None, self.mixer.reads_first())
+        if self.spec.ffn is None:
+            return resid, self.link.pending(self.mixer(xs, ctx, cache))
+        a = self.mixer(xs[0], ctx, cache)
+        return resid, self.link.pending(a, self.ffn(xs[1], ctx))
+
+
 def norm_before(norm, resid, delta, reader):
     """``norm(resid + delta)`` for the part ``reader``; a norm that takes hints is told which matrix is read next."""
     if norm.takes_hint:

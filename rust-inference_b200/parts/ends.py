@@ -5,8 +5,9 @@
 outside the table is reported through the error word (thanhauco/rust-inference
 src/ops/embedding.rs:10-42).
 
-``linear`` head: logits = x W^T, no bias, no scaling or soft-cap, float32 out of the float32
-accumulator (src/models/qwen3.rs:166-171, 286).  When the model ties its embeddings the head is
+``linear`` head: logits = x W^T, no bias, float32 out of the float32 accumulator
+(src/models/qwen3.rs:166-171, 286); a record may give a factor on the logits and a soft-cap
+(cap * tanh(logits / cap)) applied after it.  When the model ties its embeddings the head is
 given the embedding's table instead of a tensor of its own.
 
 Another architecture registers other kinds (a scaled embedding, a head with a soft-cap or a bias)
@@ -89,4 +90,5 @@ class LinearHead(Part):
         return self.weight
 
     def __call__(self, x):
-        return ops.scale_(ops.linear(x, self.weight, out_dtype=torch.float32), getattr(self.spec, "scale", 1.0))
+        z = ops.scale_(ops.linear(x, self.weight, out_dtype=torch.float32), getattr(self.spec, "scale", 1.0))
+        return ops.softcap_(z, getattr(self.spec, "softcap", 0.0))

@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import torch
 
-from .base import Part, Pending, WeightedSum
+from .base import Injection, Part, Pending, WeightedSum
 from .registry import ParamInfo, register_link
 
 
@@ -76,3 +76,50 @@ class HyperConnection(Part):
         if not terms:
             raise ValueError("a sublayer without output")
         return Pending(terms[0][0], self.mix, terms[0][1], tuple(terms[1:]))
+
+
+@register_link("pass_entry")
+class PassEntry(Part):
+    """What a pass over a repeated run of layers adds to the residual on entry: for every pass but the first the
+    embedding's output once more, and for every pass row t of a learned table [passes, hidden], in this order and in
+    float32.  Like the connection above it computes nothing itself: it wraps whatever is pending together with these
+    terms, and the norm in front of the pass's first layer adds them in the pass in which it reads the residual.
+    The embedding's rows are taken from its table again (the token ids are at hand), not from a kept copy."""
+    graph_safe = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        if spec.passes < 1:
+            raise ValueError(f"a repeated run has at least one pass, got {spec.passes}")
+        self.steps = None
+        self.embedding = None
+
+    @classmethod
+    def param_infos(cls, spec):
+        return {spec.name: ParamInfo((spec.passes, spec.hidden_size), "vector")}
+
+    def load(self, tensors):
+        self.steps = tensors[self.spec.name].contiguous()
+
+    def weight_bytes(self):
+        return 0 if self.steps is None else 4 * self.steps.numel()
+
+    def bind(self, embedding) -> None:
+        """The model's embedding part: its ``table`` and the factor of its record are what is added again."""
+        if self.spec.readd_embedding and getattr(embedding.spec, "kind", "") != "embedding":
+            raise ValueError("a pass that adds the embedding's output again needs the plain (scaled) embedding")
+        self.embedding = embedding
+
+    def __call__(self, delta, t: int, ids) -> Pending:
+        if not 0 <= t < self.spec.passes:
+            raise ValueError(f"pass {t} of {self.spec.passes}")
+        again = self.spec.readd_embedding and t > 0
+        entry = Injection(ids if again else None, self.embedding.table if again else None,
+                          float(getattr(self.embedding.spec, "scale", 1.0)) if again else 1.0, self.steps[t])
+        if delta is None:
+            return Pending(None, entry=entry)
+        if isinstance(delta, Pending):
+            if delta.entry is not None:
+                raise ValueError("two entries of a pass in front of one layer")
+            return Pending(delta.y, delta.mix, delta.out, delta.more, entry)
+        return Pending(delta, entry=entry)

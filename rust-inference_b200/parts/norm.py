@@ -66,3 +66,43 @@ class LayerNorm(Norm):
         with section("layernorm"):
             return ops.stream_norm(streams, self.gain, self.spec.eps, self.env.dtype, "layernorm", delta=y, mix=mix,
                                    out_w=out, read=read, rows=rows, bias=self.bias, more=more)
+
+
+@register_norm("rms_gains")
+class RMSGains(Norm):
+    """RMS norm of the (single-stream) residual with one gain per name of the record: one pass computes
+    1 / sqrt(mean(x^2) + eps) once and writes x times it times every gain.  The pending outputs (up to two, the sum of
+    the two taken first: x + (a + b)) and the terms of a pass's entry (:class:`~.base.Injection`) join in the same
+    pass, in float32.  Returns one tensor for one name, a tuple for several."""
+    graph_safe = True
+    takes_hint = True
+
+    @classmethod
+    def param_infos(cls, spec):
+        return {name: ParamInfo((spec.size,), "gain") for name in spec.names}
+
+    def load(self, tensors):
+        self.gains = tuple(tensors[name] for name in self.spec.names)
+        if not 1 <= len(self.gains) <= 2:
+            raise ValueError(f"rms_gains: {len(self.gains)} gains (one or two are built)")
+
+    def weight_bytes(self):
+        return sum(g.numel() * 4 for g in self.gains)
+
+    def __call__(self, resid, delta=None, rows=None, then=None):
+        terms, entry = [], None
+        if isinstance(delta, Pending):
+            if delta.mix is not None:
+                raise ValueError("rms_gains reads a residual of one stream without mixing weights")
+            if delta.y is not None:
+                terms = [(delta.y, delta.out)] + list(delta.more)
+            entry = delta.entry
+        elif delta is not None:
+            terms = [(delta, None)]
+        if resid.dim() == 3:
+            if resid.shape[1] != 1:
+                raise ValueError("rms_gains reads a residual of one stream")
+            resid = resid.view(resid.shape[0], resid.shape[2])
+        with section("rmsnorm"):
+            outs = ops.rms_gains(resid, self.gains, self.spec.eps, self.env.dtype, terms=terms, entry=entry, rows=rows, then=then)
+        return outs[0] if len(outs) == 1 else outs

@@ -10,7 +10,8 @@ the same rotary size, base, scaling and device share one table (a model's layers
 usually do), so it is held once, not once per layer.
 
 ``rope_pairs``: neighbouring elements (2i, 2i+1) are turned, not the two halves, optionally with YaRN's
-blended frequencies and its factor on cos and sin (:class:`~..config.specs.RopePairsSpec` has the rule).  The
+blended frequencies and its factor on cos and sin, or with frequencies slowed by wavelength
+(:class:`~..config.specs.RopePairsSpec` has both rules).  The
 frequencies are evaluated in float64 and rounded to float32, the angle is the float32 product with the float32
 position, cos and sin of it are evaluated in float64 and rounded once.  The table has the same layout
 [positions, rot/2, 2]; the kernels of the mixers that name this kind pair the elements accordingly.
@@ -73,6 +74,8 @@ class RopePairs(PositionEncoding):
         super().__init__(spec, env)
         if spec.rotary_dim <= 0 or spec.rotary_dim % 2:
             raise ValueError(f"rotary_dim {spec.rotary_dim} must be positive and even")
+        if spec.yarn is not None and getattr(spec, "by_wavelength", None) is not None:
+            raise ValueError("a rotation has YaRN's blend of frequencies or the rule by wavelength, not both")
         self._table = None
 
     def frequencies(self):
@@ -92,12 +95,20 @@ class RopePairs(PositionEncoding):
             ramp = np.clip((i - lo) / max(hi - lo, 0.001), 0.0, 1.0)
             f = f / factor * ramp + f * (1.0 - ramp)
             mult = 0.1 * math.log(factor) + 1.0
+        rule = getattr(self.spec, "by_wavelength", None)
+        if rule is not None:
+            factor, low, high, original = (float(v) for v in rule)
+            wave = 2.0 * math.pi / f
+            s = (original / wave - low) / (high - low) if high != low else np.ones_like(f)
+            f = np.where(wave < original / high, f, np.where(wave > original / low, f / factor,
+                                                              (1.0 - s) * f / factor + s * f))
         return f.astype(np.float32), mult
 
     def prepare(self, max_positions: int) -> None:
         if self._table is not None and self._table.shape[0] >= max_positions:
             return
-        key = (str(self.env.device), "pairs", int(self.spec.rotary_dim), float(self.spec.theta), self.spec.yarn)
+        key = (str(self.env.device), "pairs", int(self.spec.rotary_dim), float(self.spec.theta), self.spec.yarn,
+               getattr(self.spec, "by_wavelength", None))
         shared = _shared_tables.get(key)
         if shared is not None and shared.shape[0] >= max_positions:
             self._table = shared

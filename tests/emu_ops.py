@@ -15,7 +15,7 @@ import torch
 __all__ = ["embed", "rmsnorm", "add_rows", "silu_mul", "linear_swiglu", "linear", "qk_norm_rope_append", "attention", "argmax",
            "sample", "mark_seen", "stream_norm", "activation", "gate_heads", "linear_heads", "latent_prep", "gla_recurrent",
            "head_norm_gate", "linear_act", "scale_", "embed_pair_hash", "short_conv", "delta_rule_recurrent", "gated_act",
-           "linear_gated", "moe_route", "moe_plan", "moe_grouped_linear", "moe_combine"]
+           "linear_gated", "moe_route", "moe_plan", "moe_grouped_linear", "moe_combine", "rms_gains", "qkv_prep", "softcap_"]
 
 
 def embed(ids, table, scale=1.0, copies=1):
@@ -196,7 +196,8 @@ def qk_norm_rope_append(qkv, num_heads, num_kv_heads, head_dim, q_gain, k_gain, 
     return q.to(qkv.dtype).contiguous()
 
 
-def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_new, scale, window=0, sink=None, chunk=0):
+def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_new, scale, window=0, sink=None, chunk=0,
+              softcap=0.0):
     T, H, Dh = q.shape
     KV, P = k_pool.shape[1], k_pool.shape[2]
     G = H // KV
@@ -214,6 +215,8 @@ def attention(q, k_pool, v_pool, page_table, seq_slot, seq_start, seq_len, max_n
             vv = v_pool[pages, :, (idx % P).long(), :].float()
             for h in range(H):
                 s = (kk[:, h // G, :] @ q[t, h].float()) * scale
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
                 if sink is None:
                     p = torch.softmax(s, dim=0)
                 else:
@@ -379,3 +382,65 @@ def moe_combine(pair_out, idx, weight, x, experts, extra=None):
     if extra is not None:
         y += extra.float()
     return y.to(x.dtype)
+
+
+def rms_gains(resid, gains, eps, out_dtype, terms=(), entry=None, rows=None, then=None):
+    x = resid if rows is None else resid[rows.long()]
+    terms = list(terms)
+    if terms:
+        ys = [(y if rows is None else y[rows.long()]).float() * (1.0 if w is None else w[0]) for y, w in terms]
+        x = x + (ys[0] if len(ys) == 1 else ys[0] + ys[1])
+    if entry is not None:
+        if entry.ids is not None:
+            x = x + entry.table[entry.ids.long()].float() * entry.scale
+        if entry.vec is not None:
+            x = x + entry.vec
+    if rows is None and (terms or entry is not None):
+        resid.copy_(x)
+    r = 1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
+    return tuple((x * r * g).to(out_dtype) for g in gains)
+
+
+def qkv_prep(proj, q_col, k_col, v_col, heads, kv_heads, Dp, Dk, bias, rope_table, rot, pairs, unit, eps, k_pool, v_pool,
+             page_table, tok_seq, tok_pos, seq_slot, write_kv=True):
+    T = proj.shape[0]
+    x = proj.float()
+    if bias is not None:
+        x = x.clone()
+        x[:, :bias.numel()] += bias
+    q = x[:, q_col:q_col + heads * Dp].reshape(T, heads, Dp)
+    k = x[:, k_col:k_col + kv_heads * Dp].reshape(T, kv_heads, Dp)
+    v = None if v_col < 0 else x[:, v_col:v_col + kv_heads * Dp].reshape(T, kv_heads, Dp)
+
+    def turn(t):
+        if rope_table is None or not rot:
+            return t
+        cs = rope_table[tok_pos.long()]
+        c, s = cs[:, None, :, 0], cs[:, None, :, 1]
+        if pairs:
+            a, b = t[..., 0:rot:2], t[..., 1:rot:2]
+            return torch.cat([torch.stack([a * c - b * s, b * c + a * s], dim=-1).flatten(-2), t[..., rot:]], dim=-1)
+        half = rot // 2
+        lo, hi = t[..., :half], t[..., half:rot]
+        return torch.cat([lo * c - hi * s, hi * c + lo * s, t[..., rot:]], dim=-1)
+
+    def unit_rms(t):
+        return t / torch.sqrt((t * t).sum(-1, keepdim=True) / Dk + eps) if unit else t
+
+    q, k = unit_rms(turn(q)), unit_rms(turn(k))
+    if write_kv:
+        P = k_pool.shape[2]
+        for t in range(T):
+            pos = int(tok_pos[t])
+            page = int(page_table[int(seq_slot[int(tok_seq[t])]), pos // P])
+            assert page >= 0, "write to an unmapped page"
+            k_pool[page, :, pos % P, :] = k[t].to(k_pool.dtype)
+            if v is not None:
+                v_pool[page, :, pos % P, :] = v[t].to(v_pool.dtype)
+    return q.to(proj.dtype).contiguous()
+
+
+def softcap_(x, cap):
+    if cap:
+        x.copy_(cap * torch.tanh(x / cap))
+    return x

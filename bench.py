@@ -18,10 +18,11 @@ steps end at exactly 4,096 tokens.  One JSON line is printed:
   points     decode tokens a second at batch 1 and 64 (device-timed), and the same through
              the Python entry point (e2e_b1, e2e_b64)
 
-    python bench.py --design ranudra|pitenex [--size small|large]
+    python bench.py --design ranudra|pitenex|kagatar [--size small|large]
 
 measures another design (Ranudra: latent attention, gated linear attention, hyper-connections; Pitenex: chunked attention
-with a sink beside the gated delta rule, dense and routed feed-forwards) at layer sizes that
+with a sink beside the gated delta rule, dense and routed feed-forwards; Kagatar: three kinds of attention with biases
+beside a clamped-swish feed-forward behind two gains over one RMS statistic) at layer sizes that
 resemble a real model's, beside a Qwen3 model of the same width and depth: decode at batch 8 and a
 prompt step of 2,048 tokens, device-timed, and the device time of every section of both steps from eager runs with
 the section timers on, with the bytes or flops of the sections that have a roofline.  One JSON line.
@@ -300,7 +301,32 @@ def pitenex_config(z) -> dict:
             "residual_mult": 0.5, "logit_scale": 1.0, "layers": [dense, moe] * (z["layers"] // 2)}
 
 
-DESIGNS = {"ranudra": ranudra_config, "pitenex": pitenex_config}
+def kagatar_config(z) -> dict:
+    """Layers of a mixer and a clamped-swish feed-forward side by side behind two gains over one RMS statistic.  The
+    mixers take turns: gated attention over every earlier key (YaRN on half of a head), attention with unit-RMS queries
+    and keys, capped scores and a window of 1,024 keys, and attention whose values are its keys with a window of 4,096;
+    heads of 128, four query heads per key/value head.  The second half of the layers is a run of one pass (its entry
+    adds the learned vector)."""
+    D, H = z["width"], z["heads"]
+    G = max(1, H // 4)
+    inter = -(-(2 * z["ff"] // 3) // 256) * 256          # three matrices of a gated feed-forward against two
+    mlp = {"kind": "dense", "ff": inter, "limit": 7.0}
+    base = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    gated = {"type": "attention_2", "mlp": mlp,
+             "mixer": dict(base, rot={"base": 500000.0, "dims": 64,
+                                      "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}})}
+    capped = {"type": "attention_3", "mlp": mlp,
+              "mixer": dict(base, scale=1.0, softcap=50.0, mask={"size": 1024},
+                            rot={"base": 1000000.0, "dims": 128,
+                                 "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})}
+    shared = {"type": "attention", "mlp": mlp, "mixer": dict(base, mask={"size": 4096})}
+    n = z["layers"] // 3 * 3
+    return {"architecture": "Kagatar", "vocab": z["vocab"], "width": D, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "loop": {"start": n // 2, "stop": n, "times": 1},
+            "layers": [gated, capped, shared] * (z["layers"] // 3)}
+
+
+DESIGNS = {"ranudra": ranudra_config, "pitenex": pitenex_config, "kagatar": kagatar_config}
 
 
 def qwen3_like(z) -> dict:

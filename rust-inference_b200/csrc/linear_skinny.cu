@@ -78,10 +78,15 @@ struct __align__(1024) SkinnySmem {
 
 // NT: token tiles of 8 (1 or 2).  SWIGLU: the 16 rows of a block are 8 gate rows followed by their 8 up rows;
 // the block writes silu(gate) * up, 8 outputs per token, into y [M, N/2].
+// constants of the gate function 3 (clamped swish): g = min(g, limit), u = clamp(u, -limit, limit), g sigmoid(alpha g) (u + 1)
+struct SkGate {
+    float limit, alpha;
+};
+
 template <int NT, typename OutT, bool SWIGLU, int STAGES>
 __global__ void __launch_bounds__(32 * SK_WARPS, STAGES == SK_STAGES ? SK_MIN_BLOCKS : 2)
 linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ y, int M, int N,
-                     int K, int early_from, int act, int* __restrict__ err) {
+                     int K, int early_from, int act, int* __restrict__ err, SkGate gate) {
     // act (without SWIGLU): 0 nothing, 1 the square of relu, 2 gelu in its tanh form, on the float32 sums before the store
     extern __shared__ __align__(16) unsigned char sk_raw[];
     SkinnySmem<STAGES>& sm = *reinterpret_cast<SkinnySmem<STAGES>*>(sk_raw + ((1024u - (smem_u32(sk_raw) & 1023u)) & 1023u));
@@ -197,9 +202,16 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
                 g += sm.part[wi][r][tok];
                 u += sm.part[wi][r + 8][tok];
             }
-            // the gate's function: silu, or (act 2) gelu in its tanh form
-            const float fg = act == 2 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
-                                      : g / (1.0f + expf(-g));
+            // the gate's function: silu, (act 2) gelu in its tanh form, or (act 3) the clamped swish
+            float fg;
+            if (act == 3) {
+                g = fminf(g, gate.limit);
+                u = fminf(fmaxf(u, -gate.limit), gate.limit) + 1.0f;
+                fg = g / (1.0f + expf(-gate.alpha * g));
+            } else {
+                fg = act == 2 ? 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)))
+                              : g / (1.0f + expf(-g));
+            }
             st_f(y + (size_t)tok * (N / 2) + n0 / 2 + r, fg * u);
         }
     } else {
@@ -266,7 +278,7 @@ static int weight_tensor_map(const CUtensorMap** out, const void* w, int N, int 
 
 template <int NT, typename OutT, bool SWIGLU, int STAGES>
 static int launch_skinny_ring(const CUtensorMap* map, dim3 grid, int early_from, const void* x, void* y, int M, int N, int K, int act,
-                              int* err, cudaStream_t stream) {
+                              int* err, cudaStream_t stream, SkGate gate) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(linear_skinny_kernel<NT, OutT, SWIGLU, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -275,12 +287,13 @@ static int launch_skinny_ring(const CUtensorMap* map, dim3 grid, int early_from,
         configured = true;
     }
     ri_launch_pdl(linear_skinny_kernel<NT, OutT, SWIGLU, STAGES>, grid, dim3(32 * SK_WARPS), SK_SMEM_BYTES(STAGES), stream, (const bf16*)x,
-                  *map, (OutT*)y, M, N, K, early_from, act, err);
+                  *map, (OutT*)y, M, N, K, early_from, act, err, gate);
     return 0;
 }
 
 template <int NT, typename OutT, bool SWIGLU>
-static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int act, int* err, cudaStream_t stream) {
+static int launch_skinny(const void* x, const void* w, void* y, int M, int N, int K, int act, int* err, cudaStream_t stream,
+                         SkGate gate = SkGate{0.0f, 0.0f}) {
     const CUtensorMap* map = nullptr;
     int rc = weight_tensor_map(&map, w, N, K);
     if (rc) return rc;
@@ -294,11 +307,11 @@ static int launch_skinny(const void* x, const void* w, void* y, int M, int N, in
     }
 #ifndef SK_NO_DEEP_RING      // (-DSK_NO_DEEP_RING: two stages everywhere, for comparisons)
     // a grid of at most two blocks per SM: the deeper ring (its blocks are all on the SMs at once: early_from 0)
-    if ((long long)grid.x <= 2ll * sms) return launch_skinny_ring<NT, OutT, SWIGLU, SK_DEEP_STAGES>(map, grid, 0, x, y, M, N, K, act, err, stream);
+    if ((long long)grid.x <= 2ll * sms) return launch_skinny_ring<NT, OutT, SWIGLU, SK_DEEP_STAGES>(map, grid, 0, x, y, M, N, K, act, err, stream, gate);
 #endif
     const long long resident = (long long)sms * SK_MIN_BLOCKS;                // blocks on the device at once
     const int early_from = (long long)grid.x > resident ? (int)((long long)grid.x - resident) : 0;
-    return launch_skinny_ring<NT, OutT, SWIGLU, SK_STAGES>(map, grid, early_from, x, y, M, N, K, act, err, stream);
+    return launch_skinny_ring<NT, OutT, SWIGLU, SK_STAGES>(map, grid, early_from, x, y, M, N, K, act, err, stream, gate);
 }
 
 extern "C" int ri_linear_skinny_max_tokens() { return 16; }
@@ -328,18 +341,26 @@ extern "C" int ri_linear_skinny_act(const void* x, const void* w, void* y, int M
     return 0;
 }
 
-// The gated epilogue with another function of the gate: y [M, N/2] = f(gate) * up, gate 0 = silu, 2 = gelu in its tanh form.
-extern "C" int ri_linear_skinny_gated(const void* x, const void* w, void* y, int M, int N, int K, int gate, int* err_flag,
-                                      cudaStream_t stream) {
+// The gated epilogue with another function of the gate: y [M, N/2] = f(gate) * up, gate 0 = silu, 2 = gelu in its tanh form,
+// 3 = the clamped swish min(g, limit) sigmoid(alpha min(g, limit)) * (clamp(up, -limit, limit) + 1).
+extern "C" int ri_linear_skinny_gated_with(const void* x, const void* w, void* y, int M, int N, int K, int gate, float limit,
+                                           float alpha, int* err_flag, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
-    RI_REQUIRE(gate == 0 || gate == 2, "linear_skinny: gate function %d (0 silu, 2 gelu_tanh)", gate);
+    RI_REQUIRE(gate == 0 || gate == 2 || gate == 3, "linear_skinny: gate function %d (0 silu, 2 gelu_tanh, 3 clamped swish)", gate);
     RI_REQUIRE(M > 0 && M <= 16 && N > 0 && K > 0 && K % 8 == 0 && N % 16 == 0, "linear_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
     RI_REQUIRE((((uintptr_t)x | (uintptr_t)w) & 15) == 0, "linear_skinny: x and w must be 16-byte aligned");
-    const int rc = M <= 8 ? launch_skinny<1, bf16, true>(x, w, y, M, N, K, gate, err_flag, stream)
-                          : launch_skinny<2, bf16, true>(x, w, y, M, N, K, gate, err_flag, stream);
+    const SkGate g{limit, alpha};
+    const int rc = M <= 8 ? launch_skinny<1, bf16, true>(x, w, y, M, N, K, gate, err_flag, stream, g)
+                          : launch_skinny<2, bf16, true>(x, w, y, M, N, K, gate, err_flag, stream, g);
     if (rc) return rc;
     RI_CHECK_LAUNCH("linear_skinny");
     return 0;
+}
+
+extern "C" int ri_linear_skinny_gated(const void* x, const void* w, void* y, int M, int N, int K, int gate, int* err_flag,
+                                      cudaStream_t stream) {
+    RI_REQUIRE(gate == 0 || gate == 2, "linear_skinny: gate function %d (0 silu, 2 gelu_tanh)", gate);
+    return ri_linear_skinny_gated_with(x, w, y, M, N, K, gate, 0.0f, 0.0f, err_flag, stream);
 }
 
 extern "C" int ri_linear_skinny(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int swiglu,

@@ -60,6 +60,7 @@ _SIGNATURES = {
     ("linear_skinny", "ri_linear_skinny"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny_act"): [_P, _P, _P, _I, _I, _I, _I, _I, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny_gated"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
+    ("linear_skinny", "ri_linear_skinny_gated_with"): [_P, _P, _P, _I, _I, _I, _I, _F, _F, _P, _P],
     ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _F, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _F, _P, _P],
@@ -1091,7 +1092,7 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, kind: str
         return linear_swiglu(x, w_gate_up, block)
     M, K = x.shape
     N = w_gate_up.shape[0]
-    if (kind == "gelu_tanh" and x.dtype == torch.bfloat16 and block == 8 and N % 16 == 0 and _FUSED_SWIGLU
+    if (kind in ("gelu_tanh", "clamped_swish") and x.dtype == torch.bfloat16 and block == 8 and N % 16 == 0 and _FUSED_SWIGLU
             and _takes_skinny(M, N, K, x.device) and w_gate_up.shape[1] == K):
         # a handful of tokens: the weight-streaming product applies the gate to its float32 sums
         _need(x, "x")
@@ -1099,8 +1100,8 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, kind: str
         if x.data_ptr() % 16:
             x = x.clone()
         y = torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
-        _call("linear_skinny", "ri_linear_skinny_gated", x.data_ptr(), w_gate_up.data_ptr(), y.data_ptr(), M, N, K, 2,
-              error_flag(x.device).data_ptr(), _stream())
+        _call("linear_skinny", "ri_linear_skinny_gated_with", x.data_ptr(), w_gate_up.data_ptr(), y.data_ptr(), M, N, K,
+              {"gelu_tanh": 2, "clamped_swish": 3}[kind], float(limit), float(alpha), error_flag(x.device).data_ptr(), _stream())
         return y
     return gated_act(linear(x, w_gate_up), kind, block, limit, alpha)
 

@@ -536,11 +536,45 @@ __global__ void gate_heads_kernel(T* __restrict__ x, const T* __restrict__ g, lo
     }
 }
 
+// a gate per element, eight neighbouring elements per thread (16-byte loads of bfloat16)
+template <typename T>
+__global__ void gate_heads_vec8_kernel(T* __restrict__ x, const T* __restrict__ g, long long ldg, int per_tok8, int fn, size_t total8) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const size_t t = i / per_tok8;
+    const int c = (int)(i - t * per_tok8) << 3;
+    Pack8<T> a, z, o;
+    a.load(x + 8 * i);
+    z.load(g + t * ldg + c);
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float z0 = z.get(2 * j), z1 = z.get(2 * j + 1);
+        // float32: the one-element kernel's formula (the same bits); bfloat16: the fast exponential and reciprocal
+        const float s0 = sizeof(T) == 2 ? __fdividef(1.0f, 1.0f + __expf(-z0)) : 1.0f / (1.0f + expf(-z0));
+        const float s1 = sizeof(T) == 2 ? __fdividef(1.0f, 1.0f + __expf(-z1)) : 1.0f / (1.0f + expf(-z1));
+        o.set2(j, a.get(2 * j) * (fn == 1 ? z0 * s0 : s0), a.get(2 * j + 1) * (fn == 1 ? z1 * s1 : s1));
+    }
+    o.store(x + 8 * i);
+}
+
 extern "C" int ri_gate_heads(void* x, const void* g, long long ldg, int tokens, int heads, int width, int per_head, int fn,
                              int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
     RI_REQUIRE(tokens > 0 && heads > 0 && width > 0 && (fn == 0 || fn == 1), "gate_heads: bad arguments");
     const size_t total = (size_t)tokens * heads * width;
+    const long long es = dtype == RI_DTYPE_F32 ? 4 : 2;
+    if (!per_head && ((long long)heads * width) % 8 == 0 && (ldg * es) % 16 == 0 && (((uintptr_t)x | (uintptr_t)g) & 15) == 0 &&
+        (dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16)) {
+        const size_t total8 = total / 8;
+        const int per_tok8 = (int)((long long)heads * width / 8);
+        const unsigned blocks8 = (unsigned)((total8 + 255) / 256);
+        if (dtype == RI_DTYPE_F32) ri_launch_pdl(gate_heads_vec8_kernel<float>, dim3(blocks8), dim3(256), 0, stream, (float*)x, (const float*)g, ldg, per_tok8, fn, total8);
+        else ri_launch_pdl(gate_heads_vec8_kernel<__nv_bfloat16>, dim3(blocks8), dim3(256), 0, stream, (__nv_bfloat16*)x, (const __nv_bfloat16*)g, ldg, per_tok8, fn, total8);
+        RI_CHECK_LAUNCH("gate_heads");
+        return 0;
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256 < 148 * 16 ? (total + 255) / 256 : 148 * 16);
     if (dtype == RI_DTYPE_F32) ri_launch_pdl(gate_heads_kernel<float>, dim3(blocks), dim3(256), 0, stream, (float*)x, (const float*)g, ldg, heads, width, per_head, fn, total);
     else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(gate_heads_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (__nv_bfloat16*)x, (const __nv_bfloat16*)g, ldg, heads, width, per_head, fn, total);
@@ -580,6 +614,39 @@ __global__ void gated_act_kernel(const T* __restrict__ gu, T* __restrict__ out, 
     st_f(out + i, r);
 }
 
+// float32: the formulas as the one-channel kernel has them (the same bits).  bfloat16: the hardware's exponential and
+// reciprocal approximations in the two sigmoid gates, whose errors vanish in the rounding of the result to 8 bits.
+template <typename T>
+__device__ __forceinline__ float gated_of(float g, float u, int kind, float limit, float alpha) {
+    if (kind == 0) return silu_of<T>(g) * u;
+    if (kind == 1) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    if (sizeof(T) == 2) return __fdividef(g, 1.0f + __expf(-alpha * g)) * (u + 1.0f);
+    return (g / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+}
+
+// blocks of a multiple of 8 channels: eight neighbouring channels per thread (16-byte loads of bfloat16)
+template <typename T>
+__global__ void gated_act_vec8_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter, int block, size_t total8, int kind,
+                                      float limit, float alpha) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const int per_row = inter >> 3;
+    const size_t m = i / per_row;
+    const int c = (int)(i - m * per_row) << 3;
+    Pack8<T> g, u, o;
+    const int gc = (c / block) * 2 * block + c % block;
+    g.load(gu + m * 2 * inter + gc);
+    u.load(gu + m * 2 * inter + gc + block);
+#pragma unroll
+    for (int j = 0; j < 4; j++)
+        o.set2(j, gated_of<T>(g.get(2 * j), u.get(2 * j), kind, limit, alpha), gated_of<T>(g.get(2 * j + 1), u.get(2 * j + 1), kind, limit, alpha));
+    o.store(out + m * inter + c);
+}
+
 extern "C" int ri_gated_act(const void* gu, void* out, int rows, int inter, int block, int kind, float limit, float alpha,
                             int dtype, cudaStream_t stream) {
     if (rows == 0) return 0;
@@ -587,6 +654,14 @@ extern "C" int ri_gated_act(const void* gu, void* out, int rows, int inter, int 
     RI_REQUIRE(block > 0 && inter % block == 0, "gated_act: %d channels are not whole blocks of %d", inter, block);
     RI_REQUIRE(kind >= 0 && kind <= 2, "gated_act: unknown kind %d", kind);
     size_t total = (size_t)rows * inter;
+    if (block % 8 == 0 && (((uintptr_t)gu | (uintptr_t)out) & 15) == 0 && (dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16)) {
+        const size_t total8 = total / 8;
+        const unsigned blocks8 = (unsigned)((total8 + 255) / 256);
+        if (dtype == RI_DTYPE_F32) ri_launch_pdl(gated_act_vec8_kernel<float>, dim3(blocks8), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, block, total8, kind, limit, alpha);
+        else ri_launch_pdl(gated_act_vec8_kernel<__nv_bfloat16>, dim3(blocks8), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, block, total8, kind, limit, alpha);
+        RI_CHECK_LAUNCH("gated_act");
+        return 0;
+    }
     unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == RI_DTYPE_F32) ri_launch_pdl(gated_act_kernel<float>, dim3(blocks), dim3(256), 0, stream, (const float*)gu, (float*)out, inter, block, total, kind, limit, alpha);
     else if (dtype == RI_DTYPE_BF16) ri_launch_pdl(gated_act_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter, block, total, kind, limit, alpha);

@@ -34,7 +34,7 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "attention_rows": ("attention_rows.cu", "common.cuh"),
     "linear_f32": ("linear_f32.cu", "common.cuh"),
     "streams": ("streams.cu", "common.cuh"),
-    "norm_gains": ("norm_gains.cu", "common.cuh"),
+    "norm_gains": ("norm_gains.cu", "common.cuh", "linear_skinny_geometry.cuh"),
     "qkv_prep": ("qkv_prep.cu", "common.cuh"),
     "latent_attention": ("latent_attention.cu", "common.cuh"),
     "gla": ("gla.cu", "common.cuh"),

@@ -13,6 +13,7 @@
 // All arithmetic is float32 whatever T is.  The block size and the order of a row's additions depend on dim (and on
 // the pointers' alignment) only, never on how many rows a step has: a row's result is the same bits in any batch.
 #include "common.cuh"
+#include "linear_skinny_geometry.cuh"
 
 __device__ __forceinline__ float4 ng_ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 ng_ld4(const __nv_bfloat16* p) {
@@ -38,6 +39,8 @@ struct NgArgs {
     int dim, vocab, write_back;
     float scale, eps;
     int* err;
+    int n_rows;          // blocks past the rows ask for the weights that the linear after this norm reads first
+    WeightHint next;
 };
 
 // one element's new value; `e` is its index in the row
@@ -58,9 +61,10 @@ __global__ void __launch_bounds__(512) norm_gains_kernel(NgArgs a) {
     pdl_trigger();
     // parameters and the step's tables are not written by the kernel in front: read before the wait for it
     const float w1 = a.w1 ? a.w1[0] : 1.0f, w2 = a.w2 ? a.w2[0] : 1.0f;
-    const size_t r = a.rows ? (size_t)a.rows[blockIdx.x] : (size_t)blockIdx.x;
+    const bool hint_block = (int)blockIdx.x >= a.n_rows;
+    const size_t r = (a.rows && !hint_block) ? (size_t)a.rows[blockIdx.x] : (size_t)blockIdx.x;
     const T* trow = nullptr;
-    if (a.ids) {
+    if (a.ids && !hint_block) {
         const int id = a.ids[r];
         if (id < 0 || id >= a.vocab) {
             if (threadIdx.x == 0) atomicExch(a.err, 1);             // a token outside the table: its row is not added
@@ -69,6 +73,11 @@ __global__ void __launch_bounds__(512) norm_gains_kernel(NgArgs a) {
         }
     }
     pdl_wait();
+    if (hint_block) {
+        weight_hint_prefetch(a.next, ((int)blockIdx.x - a.n_rows) * (int)blockDim.x + (int)threadIdx.x,
+                             ((int)gridDim.x - a.n_rows) * (int)blockDim.x);
+        return;
+    }
     const int dim = a.dim;
     float* rp = a.resid + r * dim;
     const T* y1 = a.y1 ? (const T*)a.y1 + r * dim : nullptr;
@@ -132,11 +141,13 @@ __global__ void __launch_bounds__(512) norm_gains_kernel(NgArgs a) {
 
 // y1/w1, y2/w2: pending outputs [n, dim] of type `dtype` and their float32 factors (null: 1); ids/table/vocab/scale, vec:
 // the entry terms (each may be null); rows: int32 indices of the rows to read (null: all n_rows, with write-back);
-// gain2/out2 may be null.
+// gain2/out2 may be null.  next_w [next_n, next_k] (bfloat16, or null): the weights of the weight-streaming linear that
+// reads the first result; the kernel asks for the part of them that the linear wants first after what it holds itself
+// (a hint: it changes no result).
 extern "C" int ri_norm_gains(float* resid, const void* y1, const float* w1, const void* y2, const float* w2, const int* ids,
                              const void* table, int vocab, float scale, const float* vec, const int* rows,
                              const float* gain1, const float* gain2, void* out1, void* out2, int n_rows, int dim, float eps,
-                             int dtype, int* err_flag, cudaStream_t stream) {
+                             int dtype, const void* next_w, int next_n, int next_k, int* err_flag, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     RI_REQUIRE(n_rows > 0 && dim > 0, "norm_gains: bad sizes rows=%d dim=%d", n_rows, dim);
     RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "norm_gains: unknown dtype %d", dtype);
@@ -150,6 +161,17 @@ extern "C" int ri_norm_gains(float* resid, const void* y1, const float* w1, cons
     a.resid = resid; a.y1 = y1; a.y2 = y2; a.table = ids ? table : nullptr; a.w1 = w1; a.w2 = w2; a.vec = vec;
     a.gain1 = gain1; a.gain2 = gain2; a.ids = ids; a.rows = rows; a.out1 = out1; a.out2 = out2; a.dim = dim; a.vocab = vocab;
     a.write_back = rows ? 0 : 1; a.scale = scale; a.eps = eps; a.err = err_flag;
+    a.n_rows = n_rows;
+    a.next = make_weight_hint(nullptr, 0, 0, 0);
+    if (next_w) {
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            cudaGetDevice(&dev);
+            cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        }
+        a.next = make_weight_hint(next_w, next_n, next_k, sms);
+    }
     const uintptr_t unit = dtype == RI_DTYPE_F32 ? 15 : 7;
     const bool vec4 = dim % 4 == 0 && (((uintptr_t)resid | (uintptr_t)gain1 | (uintptr_t)gain2 | (uintptr_t)vec) & 15) == 0 &&
                       (((uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)table | (uintptr_t)out1 | (uintptr_t)out2) & unit) == 0;
@@ -161,13 +183,20 @@ extern "C" int ri_norm_gains(float* resid, const void* y1, const float* w1, cons
     } else {
         threads = dim >= 2048 ? 512 : (dim >= 512 ? 256 : 128);
     }
+    // with a hint: as many more blocks as give each thread a few requests
+    int extra = 0;
+    if (a.next.base) {
+        const long long lines = (long long)a.next.rows * SK_WARPS * (SK_HINT_STAGES * SK_STAGE_K * 2 / SK_HINT_LINE);
+        const int want = (int)((lines + (long long)threads * 2 - 1) / ((long long)threads * 2));
+        extra = want < 1 ? 1 : (want > 256 ? 256 : want);
+    }
     cudaError_t e = cudaSuccess;
 #define NG_GO(T, V)                                                                                                      \
     do {                                                                                                                 \
         if (smem > 48 * 1024)                                                                                            \
             e = cudaFuncSetAttribute(norm_gains_kernel<T, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         if (e != cudaSuccess) RI_FAIL((int)e, "norm_gains: %s", cudaGetErrorString(e));                                  \
-        ri_launch_pdl(norm_gains_kernel<T, V>, dim3(n_rows), dim3(threads), smem, stream, a);                            \
+        ri_launch_pdl(norm_gains_kernel<T, V>, dim3(n_rows + extra), dim3(threads), smem, stream, a);                           \
     } while (0)
     if (dtype == RI_DTYPE_F32) {
         if (vec4) NG_GO(float, true); else NG_GO(float, false);

@@ -48,7 +48,7 @@ _SIGNATURES = {
     ("rope_kv", "ri_qk_norm_rope_append"): [_P] * 10 + [_F, _P, _I, _I] + [_I] * 9 + [_P, _P],
     ("attention_rows", "ri_attention_rows"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _F, _I, _P, _P],
     ("elementwise", "ri_softcap_f32"): [_P, _L, _F, _P],
-    ("norm_gains", "ri_norm_gains"): [_P] * 6 + [_P, _I, _F] + [_P] * 6 + [_I, _I, _F, _I, _P, _P],
+    ("norm_gains", "ri_norm_gains"): [_P] * 6 + [_P, _I, _F] + [_P] * 6 + [_I, _I, _F, _I, _P, _I, _I, _P, _P],
     ("qkv_prep", "ri_qkv_prep"): [_P, _L, _I, _I, _I] + [_P] * 9 + [_I, _I, _I, _I, _F] + [_I] * 10 + [_P, _P],
     ("linear_f32", "ri_linear_f32"): [_P, _P, _P, _I, _I, _I, _P],
     ("sampling", "ri_sample"): [_P, _L, _I, _I, _P, _P, _L, _P, _P, _P, _P, _P, _P, _P, _L, _I, _I, _P, _I, _P],
@@ -659,7 +659,9 @@ def rms_gains(resid: torch.Tensor, gains, eps: float, out_dtype: torch.dtype, te
     outputs as pairs (tensor [n, dim] of the compute dtype, a float32 factor [1] or None for 1), two of them summed
     before they are added (x + (a + b)); then ``entry`` (an object with ``ids``, ``table``, ``scale``, ``vec``):
     table[ids] * scale (``ids`` None: not) and the vector ``vec`` [dim].  The new residual is written back unless ``rows``
-    (int32 indices: only those rows are read, in that order) is given.  ``then``: unused (a hint)."""
+    (int32 indices: only those rows are read, in that order) is given.  ``then``: the weight matrix of the linear that
+    reads the first result next; for a handful of bfloat16 rows the kernel asks for its start to be brought into L2 (a
+    hint; it changes no result)."""
     _need(resid, "resid", torch.float32)
     n, dim = resid.shape
     gains = tuple(gains)
@@ -693,10 +695,12 @@ def rms_gains(resid: torch.Tensor, gains, eps: float, out_dtype: torch.dtype, te
         _need(rows, "rows", torch.int32)
     n_out = n if rows is None else rows.numel()
     outs = tuple(torch.empty((n_out, dim), dtype=out_dtype, device=resid.device) for _ in gains)
+    hint = _weight_hint(then, n_out) if out_dtype == torch.bfloat16 else None
     _call("norm_gains", "ri_norm_gains", resid.data_ptr(), _ptr(terms[0][0]), _ptr(terms[0][1]), _ptr(terms[1][0]),
           _ptr(terms[1][1]), _ptr(ids), _ptr(table), int(vocab), scale, _ptr(vec), _ptr(rows), gains[0].data_ptr(),
           gains[1].data_ptr() if len(gains) > 1 else None, outs[0].data_ptr(), outs[1].data_ptr() if len(gains) > 1 else None,
-          n_out, dim, float(eps), _code(out_dtype), error_flag(resid.device).data_ptr(), _stream())
+          n_out, dim, float(eps), _code(out_dtype), _ptr(hint), hint.shape[0] if hint is not None else 0,
+          hint.shape[1] if hint is not None else 0, error_flag(resid.device).data_ptr(), _stream())
     return outs
 
 

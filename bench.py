@@ -313,16 +313,16 @@ def kagatar_config(z) -> dict:
     mlp = {"kind": "dense", "ff": inter, "limit": 7.0}
     base = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
     gated = {"type": "attention_2", "mlp": mlp,
-             "mixer": dict(base, rot={"base": 500000.0, "dims": 64,
-                                      "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}})}
+             "mixer": dict(base, rot={"base": 250000.0, "dims": 64,
+                                      "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}})}
     capped = {"type": "attention_3", "mlp": mlp,
               "mixer": dict(base, scale=1.0, softcap=50.0, mask={"size": 1024},
-                            rot={"base": 1000000.0, "dims": 128,
-                                 "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}})}
+                            rot={"base": 10000.0, "dims": 128,
+                                 "scaling": {"factor": 8.0, "low": 1.0, "high": 8.0, "original": 8192}})}
     shared = {"type": "attention", "mlp": mlp, "mixer": dict(base, mask={"size": 4096})}
     n = z["layers"] // 3 * 3
     return {"architecture": "Kagatar", "vocab": z["vocab"], "width": D, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
-            "logit_softcap": 30.0, "loop": {"start": n // 2, "stop": n, "times": 1},
+            "logit_softcap": 40.0, "loop": {"start": n // 2, "stop": n, "times": 1},
             "layers": [gated, capped, shared] * (z["layers"] // 3)}
 
 

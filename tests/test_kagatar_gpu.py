@@ -222,8 +222,8 @@ def test_soft_cap_on_logits():
     from rust_inference_b200 import ops
     rng = np.random.default_rng(1)
     z = rng.standard_normal((7, 333)) * 40
-    got = ops.softcap_(_t(z), 30.0)
-    _close(got, P.soft_cap(z.astype(np.float32).astype(np.float64), 30.0), torch.float32, "capped logits", tol32=1e-6)
+    got = ops.softcap_(_t(z), 18.0)
+    _close(got, P.soft_cap(z.astype(np.float32).astype(np.float64), 18.0), torch.float32, "capped logits", tol32=1e-6)
     same = _t(z)
     assert ops.softcap_(same, 0.0) is same and torch.equal(same, _t(z))
 

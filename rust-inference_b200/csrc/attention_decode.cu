@@ -395,6 +395,7 @@ struct StreamArgs {
     int seqs, KV, mpps, num_pages, window, max_pages, parts;
     int* err;
     float cap_raw;          // a soft cap on the scores in unscaled units (cap / scale), 0 for none
+    int shared_kv;          // the values are the keys (one pool given as both): a page's tile is copied once and serves as both
 };
 
 __device__ __forceinline__ int warp_sum_int(int v) { return __reduce_add_sync(0xffffffffu, v); }
@@ -631,8 +632,8 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
         }
         slot_i = slot_i + 1 == SLOTS ? 0 : slot_i + 1;
         in_flight++;
-        if (issue_v) more = stream_next<true>(ci, a, tab, cut, lane);
-        issue_v ^= 1;
+        if (issue_v || a.shared_kv) more = stream_next<true>(ci, a, tab, cut, lane);
+        if (!a.shared_kv) issue_v ^= 1;
     };
     int gave_up_slot = 0;
     unsigned gave_up_parity = 0;
@@ -719,7 +720,7 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
                 }
             }
         }
-        release_tile();
+        if (!a.shared_kv) release_tile();          // (values that are the keys: the tile stays for P V)
         if (a.cap_raw > 0.0f) {                // a soft cap on the scores (in unscaled units), before the mask
             const float inv_cap = 1.0f / a.cap_raw;
 #pragma unroll
@@ -775,7 +776,7 @@ attention_decode_stream_kernel(const bf16* __restrict__ q, const __grid_constant
                 l_run[e >> 1] += p;                       // this lane's columns; the quad is summed at the chunk's end
             }
         // ---- O[16, Dh] += P V ---------------------------------------------------------------------------
-        wait_tile();
+        if (!a.shared_kv) wait_tile();
         {
             unsigned char* vt = ring + (size_t)slot_c * ADS_SLOT_BYTES;
             if (rows < AD_PAGE) {
@@ -1130,6 +1131,7 @@ extern "C" int ri_attention_decode_cap(const void* q, const void* k_pool, const 
         a.window = window;
         a.err = err_flag;
         a.cap_raw = cap_raw;
+        a.shared_kv = k_pool == v_pool ? 1 : 0;
         // the most runs of ADS_MIN_PAGES pages that the step can have: fewer blocks than SMs, or fewer warps per
         // block (each with a deeper ring), when they do not fill the grid
         const long long runs = ((long long)seqs * KV * max_pages + ADS_MIN_PAGES - 1) / ADS_MIN_PAGES;

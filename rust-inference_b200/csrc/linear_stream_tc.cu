@@ -90,6 +90,21 @@ __device__ __forceinline__ void lt_tmem_ld16(unsigned taddr, float (&v)[16]) {
 
 __device__ __forceinline__ float lt_silu(float t) { return t / (1.0f + expf(-t)); }
 
+// constants of the gate functions: `gated` 1 silu(g) u; 2 gelu in its tanh form times u; 3 the clamped swish
+// g' sigmoid(alpha g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)
+struct LtGate {
+    float limit, alpha;
+};
+__device__ __forceinline__ float lt_gate(float g, float u, int gated, LtGate c) {
+    if (gated == 3) {
+        g = fminf(g, c.limit);
+        u = fminf(fmaxf(u, -c.limit), c.limit) + 1.0f;
+        return (g / (1.0f + expf(-c.alpha * g))) * u;
+    }
+    if (gated == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+    return lt_silu(g) * u;
+}
+
 struct LtTail {
     unsigned long long full[LT_MAX_STAGES], empty[LT_MAX_STAGES], done;
     unsigned tmem_base;
@@ -100,7 +115,7 @@ template <typename OutT>
 __global__ void __launch_bounds__(LT_THREADS)
 linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                         OutT* __restrict__ y, int M, int Mp, int N, int K, int splits, int stages, int tmem_cols,
-                        int gated, int* __restrict__ err) {
+                        int gated, int* __restrict__ err, LtGate gate_c) {
     extern __shared__ __align__(1024) unsigned char lt_smem[];
     if (smem_u32(lt_smem) & 1023u) {                               // the swizzle's period
         if (threadIdx.x == 0) atomicExch(err, 6);
@@ -219,7 +234,7 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 for (int i = 0; i < 16; i++) {
                     const float g = my_stages > 0 ? v[i] : 0.0f;
                     const float u = __shfl_down_sync(0xffffffffu, g, 8);
-                    if (gate_row && row_ok && c + i < M) st_f(y + (size_t)(c + i) * (N / 2) + ch, lt_silu(g) * u);
+                    if (gate_row && row_ok && c + i < M) st_f(y + (size_t)(c + i) * (N / 2) + ch, lt_gate(g, u, gated, gate_c));
                 }
             } else if (row_ok) {
 #pragma unroll
@@ -263,10 +278,10 @@ linear_stream_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_
                 }
             }
             OutT* dst = y + (size_t)t * (N / 2) + (n0 >> 1) + o4;
-            if (n0 + rg + 8 < N) st_f(dst, lt_silu(g.x) * u.x);
-            if (n0 + rg + 9 < N) st_f(dst + 1, lt_silu(g.y) * u.y);
-            if (n0 + rg + 10 < N) st_f(dst + 2, lt_silu(g.z) * u.z);
-            if (n0 + rg + 11 < N) st_f(dst + 3, lt_silu(g.w) * u.w);
+            if (n0 + rg + 8 < N) st_f(dst, lt_gate(g.x, u.x, gated, gate_c));
+            if (n0 + rg + 9 < N) st_f(dst + 1, lt_gate(g.y, u.y, gated, gate_c));
+            if (n0 + rg + 10 < N) st_f(dst + 2, lt_gate(g.z, u.z, gated, gate_c));
+            if (n0 + rg + 11 < N) st_f(dst + 3, lt_gate(g.w, u.w, gated, gate_c));
         }
         asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
     } else {
@@ -370,7 +385,7 @@ extern "C" int ri_linear_stream_tc_splits(int N, int K, int sms) { return lt_spl
 template <typename OutT>
 static cudaError_t lt_launch(dim3 grid, int splits, size_t smem, cudaStream_t stream, const CUtensorMap& map_w,
                              const CUtensorMap& map_x, OutT* y, int M, int Mp, int N, int K, int stages, int tmem_cols, int gated,
-                             int* err) {
+                             int* err, LtGate gate_c) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = dim3(LT_THREADS);
@@ -385,13 +400,16 @@ static cudaError_t lt_launch(dim3 grid, int splits, size_t smem, cudaStream_t st
     attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 2;
-    return cudaLaunchKernelEx(&cfg, linear_stream_tc_kernel<OutT>, map_w, map_x, y, M, Mp, N, K, splits, stages, tmem_cols, gated, err);
+    return cudaLaunchKernelEx(&cfg, linear_stream_tc_kernel<OutT>, map_w, map_x, y, M, Mp, N, K, splits, stages, tmem_cols, gated, err, gate_c);
 }
 
-// gated != 0: W [N, K] holds gate and up rows alternating in blocks of 8 and y [M, N / 2] gets silu(gate) * up
-extern "C" int ri_linear_stream_tc(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated,
-                                   int* err_flag, cudaStream_t stream) {
+// gated != 0: W [N, K] holds gate and up rows alternating in blocks of 8 and y [M, N / 2] gets f(gate, up): 1 silu(gate) * up,
+// 2 gelu_tanh(gate) * up, 3 the clamped swish with `limit` and `alpha`
+extern "C" int ri_linear_stream_tc_gate(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated,
+                                        float limit, float alpha, int* err_flag, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
+    RI_REQUIRE(gated >= 0 && gated <= 3, "linear_stream_tc: gate function %d (1 silu, 2 gelu_tanh, 3 clamped swish)", gated);
+    const LtGate gate_c{limit, alpha};
     RI_REQUIRE(M > 0 && N > 0 && K > 0, "linear_stream_tc: bad sizes M=%d N=%d K=%d", M, N, K);
     RI_REQUIRE(M <= LT_MAX_TOKENS, "linear_stream_tc: at most %d tokens, got %d", LT_MAX_TOKENS, M);
     RI_REQUIRE(K % 8 == 0, "linear_stream_tc: K=%d must be a multiple of 8", K);
@@ -425,9 +443,14 @@ extern "C" int ri_linear_stream_tc(const void* x, const void* w, void* y, int M,
         configured[out_f32 ? 1 : 0] = true;
     }
     dim3 grid(tiles, splits);
-    cudaError_t le = out_f32 ? lt_launch<float>(grid, splits, smem, stream, map_w, map_x, (float*)y, M, Mp, N, K, stages, tmem_cols, gated, err_flag)
-                             : lt_launch<bf16>(grid, splits, smem, stream, map_w, map_x, (bf16*)y, M, Mp, N, K, stages, tmem_cols, gated, err_flag);
+    cudaError_t le = out_f32 ? lt_launch<float>(grid, splits, smem, stream, map_w, map_x, (float*)y, M, Mp, N, K, stages, tmem_cols, gated, err_flag, gate_c)
+                             : lt_launch<bf16>(grid, splits, smem, stream, map_w, map_x, (bf16*)y, M, Mp, N, K, stages, tmem_cols, gated, err_flag, gate_c);
     if (le != cudaSuccess) RI_FAIL((int)le, "linear_stream_tc: %s", cudaGetErrorString(le));
     RI_CHECK_LAUNCH("linear_stream_tc");
     return 0;
+}
+
+extern "C" int ri_linear_stream_tc(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int gated,
+                                   int* err_flag, cudaStream_t stream) {
+    return ri_linear_stream_tc_gate(x, w, y, M, N, K, out_f32, gated ? 1 : 0, 0.0f, 0.0f, err_flag, stream);
 }

@@ -62,6 +62,7 @@ _SIGNATURES = {
     ("linear_skinny", "ri_linear_skinny_gated"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     ("linear_skinny", "ri_linear_skinny_gated_with"): [_P, _P, _P, _I, _I, _I, _I, _F, _F, _P, _P],
     ("linear_stream_tc", "ri_linear_stream_tc"): [_P, _P, _P, _I, _I, _I, _I, _I, _P, _P],
+    ("linear_stream_tc", "ri_linear_stream_tc_gate"): [_P, _P, _P, _I, _I, _I, _I, _I, _F, _F, _P, _P],
     ("attention_prefill_tc", "ri_attention_prefill_tc"): [_P] * 8 + [_I] * 9 + [_F, _I, _P, _F, _P, _P],
     ("attention_prefill", "ri_attention_prefill"): [_P] * 8 + [_I] * 8 + [_F, _I, _P, _I, _F, _P, _P],
 }
@@ -586,11 +587,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     return torch.mm(x, w.t())
 
 
+_STREAM_TC_GATES = {"silu": 1, "gelu_tanh": 2, "clamped_swish": 3}
+
+
 def linear_stream_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-                     gated: bool = False) -> torch.Tensor:
+                     gated: bool = False, gate: str = "silu", limit: float = 0.0, alpha: float = 1.0) -> torch.Tensor:
     """y = x w^T in bfloat16 for up to 128 tokens on tcgen05: weight rows as the M side of the product, tokens as N,
     K split over a thread-block cluster whose partial tiles are added through distributed shared memory.
-    ``gated``: w holds gate and up rows alternating in blocks of 8, and y [M, N/2] = silu(gate) * up."""
+    ``gated``: w holds gate and up rows alternating in blocks of 8, and y [M, N/2] = f(gate) * up' with the gate function
+    ``gate`` ("silu", "gelu_tanh", or "clamped_swish" with ``limit`` and ``alpha``: see ``gated_act``)."""
     _need(x, "x", torch.bfloat16)
     _need(w, "w", torch.bfloat16)
     M, K = x.shape
@@ -601,8 +606,9 @@ def linear_stream_tc(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch
         raise KernelError(f"linear_stream_tc: {N} gate and up rows are not whole blocks of 8 and 8")
     y = torch.empty((M, N // 2 if gated else N), dtype=torch.float32 if out_dtype == torch.float32 else torch.bfloat16,
                     device=x.device)
-    _call("linear_stream_tc", "ri_linear_stream_tc", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
-          1 if out_dtype == torch.float32 else 0, 1 if gated else 0, error_flag(x.device).data_ptr(), _stream())
+    _call("linear_stream_tc", "ri_linear_stream_tc_gate", x.data_ptr(), w.data_ptr(), y.data_ptr(), M, N, K,
+          1 if out_dtype == torch.float32 else 0, _STREAM_TC_GATES[gate] if gated else 0, float(limit), float(alpha),
+          error_flag(x.device).data_ptr(), _stream())
     return y
 
 
@@ -1090,12 +1096,20 @@ def gated_act(gate_up: torch.Tensor, kind: str, block: Optional[int] = None, lim
 
 def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, kind: str = "silu", limit: float = 0.0,
                  alpha: float = 1.0) -> torch.Tensor:
-    """f(x Wg^T) * (x Wu^T)' for the stacked matrix of ``linear_swiglu``; "silu" takes that function's fused kernels,
-    the other gates (see ``gated_act``) run the product and the gate one after the other."""
+    """f(x Wg^T) * (x Wu^T)' for the stacked matrix of ``linear_swiglu``; "silu" takes that function's fused kernels; the
+    other gates (see ``gated_act``) take the same weight-streaming kernels with the gate in their epilogues for up to 32
+    bfloat16 tokens (in the same order of choice), and run the product and the gate one after the other beyond."""
     if kind == "silu":
         return linear_swiglu(x, w_gate_up, block)
     M, K = x.shape
     N = w_gate_up.shape[0]
+    fusable = (kind in _STREAM_TC_GATES and x.dtype == torch.bfloat16 and block == 8 and N % 16 == 0 and K % 8 == 0
+               and _FUSED_SWIGLU and w_gate_up.shape[1] == K)
+    if fusable and _gated_on_stream_tc(M, N, K, x.device):
+        # a large matrix and a few tokens: the tcgen05 weight-streaming product, the gate in its epilogue
+        return linear_stream_tc(x, w_gate_up, gated=True, gate=kind, limit=limit, alpha=alpha)
+    if fusable and not _takes_skinny(M, N, K, x.device) and _takes_stream_tc(M, N, K):
+        return linear_stream_tc(x, w_gate_up, gated=True, gate=kind, limit=limit, alpha=alpha)
     if (kind in ("gelu_tanh", "clamped_swish") and x.dtype == torch.bfloat16 and block == 8 and N % 16 == 0 and _FUSED_SWIGLU
             and _takes_skinny(M, N, K, x.device) and w_gate_up.shape[1] == K):
         # a handful of tokens: the weight-streaming product applies the gate to its float32 sums

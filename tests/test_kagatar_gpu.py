@@ -209,13 +209,24 @@ def test_clamped_swish_feed_forward_gate_behind_a_product(dtype):
     inter, Kd = 40, 64
     wg, wu = _t(rng.standard_normal((inter, Kd)) * 0.3, dtype), _t(rng.standard_normal((inter, Kd)) * 0.3, dtype)
     stacked = torch.stack([wg.view(inter // 8, 8, Kd), wu.view(inter // 8, 8, Kd)], dim=1).reshape(2 * inter, Kd).contiguous()
-    for m in (1, 3, 12, 70):
+    for m in (1, 3, 12, 20, 32, 70):                     # (13 to 32 bfloat16 tokens: the tcgen05 weight-streaming product)
         for limit in (0.8, 30.0):
             xin = _t(rng.standard_normal((m, Kd)), dtype)
             g = np.minimum(_np(xin) @ _np(wg).T, limit)
             u = np.clip(_np(xin) @ _np(wu).T, -limit, limit)
             got = ops.linear_gated(xin, stacked, 8, "clamped_swish", limit, 1.702)
             _close(got, g * P.sigmoid(1.702 * g) * (u + 1.0), dtype, f"{m} tokens, limit {limit}")
+    if dtype == torch.bfloat16:
+        # a matrix large enough for the tcgen05 product at a handful of tokens (K split over a cluster), both other gates
+        inter, Kd, m = 11008, 4096, 8
+        wg, wu = _t(rng.standard_normal((inter, Kd)) * 0.02, dtype), _t(rng.standard_normal((inter, Kd)) * 0.02, dtype)
+        stacked = torch.stack([wg.view(inter // 8, 8, Kd), wu.view(inter // 8, 8, Kd)], dim=1).reshape(2 * inter, Kd).contiguous()
+        xin = _t(rng.standard_normal((m, Kd)), dtype)
+        gz, uz = _np(xin) @ _np(wg).T, _np(xin) @ _np(wu).T
+        g, u = np.minimum(gz, 1.0), np.clip(uz, -1.0, 1.0)
+        _close(ops.linear_gated(xin, stacked, 8, "clamped_swish", 1.0, 1.702), g * P.sigmoid(1.702 * g) * (u + 1.0), dtype, "large")
+        gelu = 0.5 * gz * (1.0 + np.tanh(np.sqrt(2.0 / np.pi) * (gz + 0.044715 * gz ** 3)))
+        _close(ops.linear_gated(xin, stacked, 8, "gelu_tanh"), gelu * uz, dtype, "large, gelu")
 
 
 def test_soft_cap_on_logits():

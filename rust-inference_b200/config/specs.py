@@ -29,11 +29,13 @@ class RMSNormSpec:
 class RMSGainsSpec:
     """One RMS statistic, several gains: y_k = x / sqrt(mean(x^2) + eps) * gain_k for every name in ``names`` (the
     gains' local tensor names; an empty name is the norm's prefix alone).  The sublayers of a layer that all read
-    the same residual through norms of their own get their inputs from one pass over it."""
+    the same residual through norms of their own get their inputs from one pass over it.  ``one_plus``: the tensors
+    are stored around zero and the gain is 1 + tensor."""
     size: int
     eps: float
     names: Tuple[str, ...] = ("",)
     kind: str = "rms_gains"
+    one_plus: bool = False
 
 
 @dataclass(frozen=True)
@@ -74,13 +76,15 @@ class RopeSpec:
     """Rotate-half rotary encoding of the first ``rotary_dim`` elements of a head.
 
     ``theta`` is the base; angles are float32(position) * float32(inv_freq) and
-    ``scaling`` multiplies cos and sin (1.0 for the "default" rope type).
+    ``scaling`` multiplies cos and sin (1.0 for the "default" rope type).  ``freq64``: the frequencies
+    theta^(-2i/rotary_dim) are evaluated in float64 and rounded to float32 once (default: float32 power).
     """
     head_dim: int
     theta: float
     rotary_dim: int = 0          # 0 means the whole head
     scaling: float = 1.0
     kind: str = "rope"
+    freq64: bool = False
 
     @property
     def rot(self) -> int:
@@ -110,7 +114,11 @@ class AttentionSpec:
     ``unit_rms``: queries and keys are divided by their root mean square over the head (eps ``unit_eps``, no gain)
     AFTER the position encoding.  ``softcap`` > 0: score <- softcap * tanh(score / softcap) after the scale.
     ``gate``: "element" multiplies the heads' outputs element by element with the sigmoid of a projection of the
-    mixer's input (tensor ``gate_name``) before the output projection; "" for none.
+    mixer's input (tensor ``gate_name``) before the output projection; "head": one such gate per head (a projection
+    of ``num_heads`` rows); "" for none.
+    ``qk_norm_span``: "head" (the norm runs over each head's elements, one gain of the head's size for all heads) or
+    "all" (over the whole q projection, and the whole k projection, of a token at once, gains of those sizes);
+    ``qk_norm_names``: the two gains' local tensor names.
     """
     hidden_size: int
     num_heads: int
@@ -133,6 +141,8 @@ class AttentionSpec:
     softcap: float = 0.0
     gate: str = ""
     gate_name: str = "g"
+    qk_norm_span: str = "head"
+    qk_norm_names: Tuple[str, str] = ("q_norm.weight", "k_norm.weight")
 
 
 @dataclass(frozen=True)
@@ -196,6 +206,23 @@ class GatedDeltaSpec:
 
 
 @dataclass(frozen=True)
+class MLSTMSpec:
+    """The matrix memory of xLSTM: per head a state S [dim, vdim], a vector n [dim] and a running maximum m, all
+    float32.  With log input and forget gates li = cap tanh((Wi h + bi) / cap), lf = log_sigmoid(cap tanh((Wf h + bf) /
+    cap)) (``gate_cap``): m_t = max(lf + m_(t-1), li), S_t = exp(lf + m_(t-1) - m_t) S_(t-1) + exp(li - m_t) k v^T, n_t
+    likewise with k alone, o = S_t^T q / (max(|n_t . q|, exp(-m_t)) + 1e-6) with q scaled by dim^(-1/2).  Each head's o is
+    divided by its root mean square (``eps``), the heads' concatenation multiplied by a gain of that size and by the
+    sigmoid of a projection, and projected back."""
+    hidden_size: int
+    num_heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+    eps: float
+    kind: str = "mlstm"
+
+
+@dataclass(frozen=True)
 class ParallelMixerSpec:
     """Two mixers side by side on the same input: ``left_scale`` * left + ``right_scale`` * right.  Their tensors
     carry the prefixes "left." and "right."."""
@@ -223,7 +250,12 @@ class MoESpec:
     """A routed feed-forward: ``experts`` gated feed-forwards (record ``expert``, tensors "e<i>.") of which a token
     uses ``top``; the router also has ``identity`` outputs after the experts' whose "expert" returns its input.
     Scores are the softmax over all router outputs; the choice adds a learned correction to them, the weights are the
-    chosen scores divided by their sum.  ``shared`` (or None): a feed-forward that every token takes, added."""
+    chosen scores divided by their sum.  ``shared`` (or None): a feed-forward that every token takes, added.
+
+    ``score`` "sigmoid": a score is the sigmoid of its router output alone.  ``groups`` > 1: the router's outputs form
+    that many equal groups of neighbours; a group's score is the sum of its ``group_top`` largest choice scores (score
+    plus correction), and only experts of the ``group_keep`` best groups can be chosen.  ``renormalize`` False: the
+    weights are the chosen scores as they are; ``route_scale`` multiplies them."""
     hidden_size: int
     experts: int
     top: int
@@ -231,11 +263,18 @@ class MoESpec:
     identity: int = 0
     shared: object = None
     kind: str = "moe"
+    score: str = "softmax"
+    groups: int = 1
+    group_keep: int = 1
+    group_top: int = 2
+    renormalize: bool = True
+    route_scale: float = 1.0
 
 
 @dataclass(frozen=True)
 class DenseFFSpec:
-    """down(act(up x)), no biases; ``activation``: "relu2" (the square of relu) or "gelu_tanh"."""
+    """down(act(up x)), no biases; ``activation``: "relu2" (the square of relu), "gelu_tanh" or "gelu" (the exact
+    form with erf)."""
     hidden_size: int
     intermediate_size: int
     activation: str = "relu2"
@@ -251,6 +290,21 @@ class HyperConnectionSpec:
     learned: bool = True
     kind: str = "hyper"
     scale: float = 1.0          # without weights: x <- x + scale * y
+
+
+@dataclass(frozen=True)
+class PostNormSpec:
+    """How a sublayer's output joins a single-stream residual when a norm stands BEHIND the sublayer:
+    x <- x + scale * (y / sqrt(mean(y^2) + eps) * gain), y the sublayer's output (a weighted sum of several outputs is
+    taken first).  ``gain_name``: the gain's tensor; ``one_plus``: it is stored around zero (gain = 1 + tensor);
+    ``scale_name``: a vector of the residual's size that multiplies the normed output element by element (a layer
+    scale), "" for none."""
+    size: int
+    eps: float
+    gain_name: str
+    scale_name: str = ""
+    one_plus: bool = False
+    kind: str = "post_norm"
 
 
 @dataclass(frozen=True)
@@ -369,6 +423,37 @@ class ParallelNormsLayerSpec:
 
     def prefix(self, part: str) -> str:
         return dict(self.names).get(part, "")
+
+
+@dataclass(frozen=True)
+class SandwichLayerSpec:
+    """One block with a norm in front of and behind each sublayer (``arrangement`` "sandwich"):
+    x <- x + link1(mixer(norm1(x))), then (``ffn`` not None) x <- x + link2(ffn(norm2(x))).  ``mixer_norm`` and
+    ``ffn_norm`` are norms in front (:class:`RMSGainsSpec` with one name), ``mixer_link`` and ``ffn_link`` the norms
+    behind with their layer scales (:class:`PostNormSpec`).  ``names`` maps the parts to the prefixes of their tensors."""
+    mixer: object
+    mixer_norm: object
+    mixer_link: object
+    ffn: object = None
+    ffn_norm: object = None
+    ffn_link: object = None
+    names: Tuple[Tuple[str, str], ...] = ()
+    arrangement: str = "sandwich"
+
+    def prefix(self, part: str) -> str:
+        return dict(self.names).get(part, "")
+
+
+@dataclass(frozen=True)
+class PassMixSpec:
+    """What happens to the residual right before the first layer of a pass over a repeated run of layers: it is
+    replaced by a projection of itself and the embedding's output side by side, x <- W [x; x0] (tensor ``in_name``
+    [hidden, 2 hidden], x first), and then row t of the tensor ``step_name`` [passes, hidden] is added for pass t."""
+    passes: int
+    hidden_size: int
+    in_name: str = "loop.in"
+    step_name: str = "loop.step"
+    kind: str = "pass_mix"
 
 
 @dataclass(frozen=True)

@@ -38,6 +38,7 @@ SOURCES: Dict[str, Tuple[str, ...]] = {
     "qkv_prep": ("qkv_prep.cu", "common.cuh"),
     "latent_attention": ("latent_attention.cu", "common.cuh"),
     "gla": ("gla.cu", "common.cuh"),
+    "mlstm": ("mlstm.cu", "common.cuh"),
     "pair_embedding": ("pair_embedding.cu", "common.cuh"),
     "delta_rule": ("delta_rule.cu", "common.cuh"),
     "moe": ("moe.cu", "common.cuh", "mma_helpers.cuh"),

@@ -77,6 +77,44 @@ extern "C" int ri_embed_rows_scaled(const int* ids, const void* table, float* ou
     return 0;
 }
 
+// out[t, 0 .. dim) = table[ids[t]] in the table's own type, the rows of `out` `pitch` elements apart (the right half of a
+// wider matrix that a product reads next).  An id outside the table is reported and its row left as it is.
+template <typename T>
+__global__ void embed_rows_same_kernel(const int* __restrict__ ids, const T* __restrict__ table, T* __restrict__ out,
+                                       long long pitch, int dim, int vocab, int* __restrict__ bad) {
+    pdl_trigger();
+    const int id = ids[blockIdx.x];
+    pdl_wait();
+    if (id < 0 || id >= vocab) {
+        if (threadIdx.x == 0) atomicExch(bad, 1);
+        return;
+    }
+    const T* src = table + (size_t)id * dim;
+    T* dst = out + (size_t)blockIdx.x * pitch;
+    constexpr int PER = 16 / (int)sizeof(T);
+    if (dim % PER == 0 && pitch % PER == 0 && ((((uintptr_t)table | (uintptr_t)out)) & 15) == 0) {
+        for (int i = threadIdx.x * PER; i < dim; i += blockDim.x * PER)
+            *reinterpret_cast<uint4*>(dst + i) = *reinterpret_cast<const uint4*>(src + i);
+        return;
+    }
+    for (int i = threadIdx.x; i < dim; i += blockDim.x) dst[i] = src[i];
+}
+
+extern "C" int ri_embed_rows_same(const int* ids, const void* table, void* out, long long pitch, int tokens, int dim, int vocab,
+                                  int dtype, int* bad_flag, cudaStream_t stream) {
+    if (tokens == 0) return 0;
+    RI_REQUIRE(tokens > 0 && dim > 0 && vocab > 0 && pitch >= dim, "embed_rows_same: bad sizes tokens=%d dim=%d vocab=%d", tokens, dim, vocab);
+    const int threads = dim >= 1024 ? 256 : 128;
+    if (dtype == RI_DTYPE_F32)
+        ri_launch_pdl(embed_rows_same_kernel<float>, dim3(tokens), dim3(threads), 0, stream, ids, (const float*)table, (float*)out, pitch, dim, vocab, bad_flag);
+    else if (dtype == RI_DTYPE_BF16)
+        ri_launch_pdl(embed_rows_same_kernel<__nv_bfloat16>, dim3(tokens), dim3(threads), 0, stream, ids, (const __nv_bfloat16*)table, (__nv_bfloat16*)out, pitch, dim, vocab, bad_flag);
+    else
+        RI_FAIL(-1, "embed_rows_same: unknown dtype %d", dtype);
+    RI_CHECK_LAUNCH("embed_rows_same");
+    return 0;
+}
+
 extern "C" int ri_embed_rows(const int* ids, const void* table, float* out, int tokens, int dim, int vocab,
                              int dtype, int* bad_flag, cudaStream_t stream) {
     return ri_embed_rows_scaled(ids, table, out, tokens, dim, vocab, 1.0f, 1, dtype, bad_flag, stream);
@@ -465,15 +503,18 @@ extern "C" int ri_silu_mul(const void* gu, void* out, int rows, int inter, int b
 
 // ---------------------------------------------------------------------------
 // out[i] = act(x[i]):  kind 0: relu(x)^2;  kind 1: gelu with the tanh form,
-// 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))).  float32 arithmetic, one rounding at the end.
+// 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)));  kind 2: the exact gelu 0.5 x (1 + erf(x / sqrt(2))).
+// float32 arithmetic, one rounding at the end.
 // ---------------------------------------------------------------------------
 #define RI_ACT_RELU2 0
 #define RI_ACT_GELU_TANH 1
+#define RI_ACT_GELU_ERF 2
 __device__ __forceinline__ float act_of(float x, int kind) {
     if (kind == RI_ACT_RELU2) {
         const float r = fmaxf(x, 0.0f);
         return r * r;
     }
+    if (kind == RI_ACT_GELU_ERF) return 0.5f * x * (1.0f + erff(x * 0.7071067811865476f));
     return 0.5f * x * (1.0f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
 }
 
@@ -500,7 +541,7 @@ __global__ void activation_vec8_kernel(const T* __restrict__ x, T* __restrict__ 
 
 extern "C" int ri_activation(const void* x, void* out, long long n, int kind, int dtype, cudaStream_t stream) {
     if (n == 0) return 0;
-    RI_REQUIRE(n > 0 && (kind == RI_ACT_RELU2 || kind == RI_ACT_GELU_TANH), "activation: bad arguments n=%lld kind=%d", n, kind);
+    RI_REQUIRE(n > 0 && kind >= RI_ACT_RELU2 && kind <= RI_ACT_GELU_ERF, "activation: bad arguments n=%lld kind=%d", n, kind);
     RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "activation: unknown dtype %d", dtype);
     if (n % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
         const size_t n8 = (size_t)n / 8;

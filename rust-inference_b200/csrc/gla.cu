@@ -12,6 +12,13 @@
 // are widened once.  A token's result depends on the tokens before it only through the state, so prompts,
 // pieces of prompts and single tokens give the same bits.
 //
+// The same kernels run a second form (`gates` given): one decay per token and head instead of one per key channel, and
+// a factor on the key,
+//   S_t[d, j] = a_t S_(t-1)[d, j] + (b_t k_t[d]) v_t[j],      (a_t, b_t) = gates[t, h, 0..1], float32, made by the caller,
+// optionally with one more column j = vdim whose value is 1 for every token (`ones`): that column of the state is the
+// running sum n_t = a_t n_(t-1) + b_t k_t, and its output n_t . q_t, which a normaliser behind the kernel reads.  State
+// and output are then [.., vdim + 1] wide.
+//
 //   proj [tokens, ld]: q of head h at columns q_col + h dim .., k at k_col + h dim .., v at v_col + h vdim ..
 //   z    [tokens, H dim] (the low-rank decay projection, bias not yet added);  bias [H dim] float32
 //   state [slots, H, dim, vdim] float32;  o [tokens, H, vdim] float32
@@ -53,7 +60,9 @@ __global__ void __launch_bounds__(GLA_COLS)
 gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, int k_col, int v_col,
                          const T* __restrict__ z, const float* __restrict__ bias, float inv_tau, float qscale,
                          float* __restrict__ state, float* __restrict__ o, const int* __restrict__ seq_slot,
-                         const int* __restrict__ seq_start, int H, int dim, int vdim) {
+                         const int* __restrict__ seq_start, int H, int dim, int vdim_in, const float* __restrict__ gates,
+                         int gate_pitch, int ones) {
+    const int vdim = vdim_in + ones;                                         // columns of the state and of the output
     constexpr int PARTS = GLA_SPLIT * GLA_WARPS;
     constexpr int CH = DIMC / PARTS;                                         // channels per thread
     constexpr int BCOLS = GLA_BCOLS;                                         // columns per block
@@ -78,7 +87,7 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
 #pragma unroll
     for (int e = 0; e < PER; e++) {
         const int d = (threadIdx.x + e * GLA_COLS) % DIMC;
-        bs[e] = d < dim ? bias[h * dim + d] : 0.0f;
+        bs[e] = (d < dim && !gates) ? bias[h * dim + d] : 0.0f;
     }
     pdl_wait();
     float* st = state + ((size_t)slot * H + h) * dim * vdim;
@@ -91,15 +100,22 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
     // as they come from memory (widened only when they are stored into a buffer, so that nothing waits for a load
     // before the group at hand has been computed)
     T rz[PER], rk[PER], rq[PER], rv[VPER];
+    float ra[PER], rb[PER];                   // the second form's decay and key factor of the element's token
     auto fetch = [&](int base) {              // the raw values of tokens base .. base + GROUP - 1 into registers
 #pragma unroll
         for (int e = 0; e < PER; e++) {
             const int idx = threadIdx.x + e * GLA_COLS;
             const int g = idx / DIMC, d = idx % DIMC, t = base + g;
             rz[e] = rk[e] = rq[e] = T(0.0f);
+            ra[e] = rb[e] = 1.0f;
             if (g < GROUP && t < t1 && d < dim) {
                 const T* row = proj + (size_t)t * ld;
-                rz[e] = z[((size_t)t * H + h) * dim + d];
+                if (gates) {
+                    ra[e] = gates[((size_t)t * H + h) * gate_pitch];
+                    rb[e] = gates[((size_t)t * H + h) * gate_pitch + 1];
+                } else {
+                    rz[e] = z[((size_t)t * H + h) * dim + d];
+                }
                 rk[e] = row[k_col + h * dim + d];
                 rq[e] = row[q_col + h * dim + d];
             }
@@ -110,7 +126,8 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
             const int idx = threadIdx.x + e * GLA_COLS;
             const int g = idx / BCOLS, jj = blockIdx.x * BCOLS + idx % BCOLS;
             rv[e] = T(0.0f);
-            if (g < GROUP && base + g < t1 && jj < vdim) rv[e] = proj[(size_t)(base + g) * ld + v_col + h * vdim + jj];
+            if (g < GROUP && base + g < t1 && jj < vdim_in) rv[e] = proj[(size_t)(base + g) * ld + v_col + h * vdim_in + jj];
+            else if (g < GROUP && base + g < t1 && jj < vdim) rv[e] = T(1.0f);          // the column of ones
         }
     };
     auto store = [&](int buf, int base) {     // ... and from there into a buffer
@@ -121,8 +138,8 @@ gla_recurrent_reg_kernel(const T* __restrict__ proj, long long ld, int q_col, in
             if (g < GROUP) {
                 // a token past the sequence's end: decay 1, key 0 (the state stays); a channel past dim: all zero
                 const bool live = base + g < t1;
-                stage[buf][g][0][d] = d < dim ? (live ? gla_decay(ld_f(&rz[e]) + bs[e], inv_tau) : 1.0f) : 0.0f;
-                stage[buf][g][1][d] = ld_f(&rk[e]);
+                stage[buf][g][0][d] = d < dim ? (live ? (gates ? ra[e] : gla_decay(ld_f(&rz[e]) + bs[e], inv_tau)) : 1.0f) : 0.0f;
+                stage[buf][g][1][d] = gates ? ld_f(&rk[e]) * rb[e] : ld_f(&rk[e]);
                 stage[buf][g][2][d] = ld_f(&rq[e]) * qscale;
             }
         }
@@ -202,7 +219,8 @@ __global__ void __launch_bounds__(GLA_TILE)
 gla_recurrent_kernel(const T* __restrict__ proj, long long ld, int q_col, int k_col, int v_col, const T* __restrict__ z,
                      const float* __restrict__ bias, float inv_tau, float qscale, float* __restrict__ state,
                      float* __restrict__ o, const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int H,
-                     int dim, int vdim) {
+                     int dim, int vdim_in, const float* __restrict__ gates, int gate_pitch, int ones) {
+    const int vdim = vdim_in + ones;
     extern __shared__ float gla_smem[];
     float* S = gla_smem;                              // [dim][GLA_TILE]
     float* tok = S + (size_t)dim * GLA_TILE;          // two buffers of [3][dim]: decay, key, query
@@ -218,12 +236,14 @@ gla_recurrent_kernel(const T* __restrict__ proj, long long ld, int q_col, int k_
     for (int t = t0; t < t1; t++) {
         float* cur = tok + (size_t)((t - t0) & 1) * 3 * dim;
         const T* row = proj + (size_t)t * ld;
+        const float ga = gates ? gates[((size_t)t * H + h) * gate_pitch] : 1.0f;
+        const float gb = gates ? gates[((size_t)t * H + h) * gate_pitch + 1] : 1.0f;
         for (int d = threadIdx.x; d < dim; d += GLA_TILE) {
-            cur[d] = gla_decay(ld_f(z + ((size_t)t * H + h) * dim + d) + bias[h * dim + d], inv_tau);
-            cur[dim + d] = ld_f(row + k_col + h * dim + d);
+            cur[d] = gates ? ga : gla_decay(ld_f(z + ((size_t)t * H + h) * dim + d) + bias[h * dim + d], inv_tau);
+            cur[dim + d] = gates ? ld_f(row + k_col + h * dim + d) * gb : ld_f(row + k_col + h * dim + d);
             cur[2 * dim + d] = ld_f(row + q_col + h * dim + d) * qscale;
         }
-        const float v = mine ? ld_f(row + v_col + h * vdim + j) : 0.0f;
+        const float v = !mine ? 0.0f : (j < vdim_in ? ld_f(row + v_col + h * vdim_in + j) : 1.0f);
         __syncthreads();              // the token's vectors are there (the other buffer is free again after this barrier)
         float acc = 0.0f;
         for (int d = 0; d < dim; d++) {
@@ -237,13 +257,15 @@ gla_recurrent_kernel(const T* __restrict__ proj, long long ld, int q_col, int k_
         for (int d = 0; d < dim; d++) st[(size_t)d * vdim + j] = S[d * GLA_TILE + threadIdx.x];
 }
 
-extern "C" int ri_gla_recurrent(const void* proj, long long ld, int q_col, int k_col, int v_col, const void* z,
-                                const float* bias, float tau, float qscale, float* state, float* o, const int* seq_slot,
-                                const int* seq_start, int seqs, int H, int dim, int vdim, int single, int dtype,
-                                cudaStream_t stream) {
+static int gla_recurrent_go(const void* proj, long long ld, int q_col, int k_col, int v_col, const void* z,
+                            const float* bias, float tau, float qscale, float* state, float* o, const int* seq_slot,
+                            const int* seq_start, int seqs, int H, int dim, int vdim_in, int single, int dtype,
+                            const float* gates, int gate_pitch, int ones, cudaStream_t stream) {
     // single: every sequence brings one token (a smaller staging group; the same results)
     if (seqs == 0) return 0;
-    RI_REQUIRE(seqs > 0 && H > 0 && dim > 0 && vdim > 0 && tau > 0.0f, "gla_recurrent: bad sizes");
+    const int vdim = vdim_in + ones;                 // what the grid covers
+    RI_REQUIRE(seqs > 0 && H > 0 && dim > 0 && vdim_in > 0 && tau > 0.0f, "gla_recurrent: bad sizes");
+    RI_REQUIRE(gates ? gate_pitch >= 2 : (z && bias && !ones), "gla_recurrent: a decay per channel (z, bias) or per token (gates)");
     RI_REQUIRE(seqs <= 65535 && H <= 65535, "gla_recurrent: %d sequences, %d heads: too many for one launch", seqs, H);
     RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "gla_recurrent: unknown dtype %d", dtype);
     if (dim <= 128) {
@@ -258,7 +280,7 @@ extern "C" int ri_gla_recurrent(const void* proj, long long ld, int q_col, int k
             if (e != cudaSuccess) RI_FAIL((int)e, "gla_recurrent: %s", cudaGetErrorString(e));                             \
             ri_launch_pdl(gla_recurrent_reg_kernel<T, DIMC, GROUP>, grid, dim3(threads), sm, stream, (const T*)proj, ld,   \
                           q_col, k_col, v_col, (const T*)z, bias, 1.0f / tau, qscale, state, o, seq_slot, seq_start, H,    \
-                          dim, vdim);                                                                                      \
+                          dim, vdim_in, gates, gate_pitch, ones);                                                          \
         } while (0)
     // tokens staged together: many, so that a trip to memory is paid once per 32 (16) tokens
 #define GLA_REG(T, DIMC)                                                                                                   \
@@ -288,13 +310,33 @@ extern "C" int ri_gla_recurrent(const void* proj, long long ld, int q_col, int k
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(gla_recurrent_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
         if (e != cudaSuccess) RI_FAIL((int)e, "gla_recurrent: %s", cudaGetErrorString(e));                                 \
         ri_launch_pdl(gla_recurrent_kernel<T>, grid, dim3(GLA_TILE), smem, stream, (const T*)proj, ld, q_col, k_col, v_col, \
-                      (const T*)z, bias, 1.0f / tau, qscale, state, o, seq_slot, seq_start, H, dim, vdim);                 \
+                      (const T*)z, bias, 1.0f / tau, qscale, state, o, seq_slot, seq_start, H, dim, vdim_in, gates,        \
+                      gate_pitch, ones);                                                                                   \
     } while (0)
     if (dtype == RI_DTYPE_F32) GLA_GO(float);
     else GLA_GO(__nv_bfloat16);
 #undef GLA_GO
     RI_CHECK_LAUNCH("gla_recurrent");
     return 0;
+}
+
+extern "C" int ri_gla_recurrent(const void* proj, long long ld, int q_col, int k_col, int v_col, const void* z,
+                                const float* bias, float tau, float qscale, float* state, float* o, const int* seq_slot,
+                                const int* seq_start, int seqs, int H, int dim, int vdim, int single, int dtype,
+                                cudaStream_t stream) {
+    return gla_recurrent_go(proj, ld, q_col, k_col, v_col, z, bias, tau, qscale, state, o, seq_slot, seq_start, seqs, H, dim,
+                            vdim, single, dtype, nullptr, 0, 0, stream);
+}
+
+// The second form: gates [tokens, H, gate_pitch] float32 with the decay at [0] and the key's factor at [1]; ones: the
+// state [slots, H, dim, vdim + 1] and the output [tokens, H, vdim + 1] carry the column of ones.
+extern "C" int ri_gla_recurrent_scalar(const void* proj, long long ld, int q_col, int k_col, int v_col, const float* gates,
+                                       int gate_pitch, int ones, float qscale, float* state, float* o, const int* seq_slot,
+                                       const int* seq_start, int seqs, int H, int dim, int vdim, int single, int dtype,
+                                       cudaStream_t stream) {
+    RI_REQUIRE(gates != nullptr && (ones == 0 || ones == 1), "gla_recurrent_scalar: gates are needed");
+    return gla_recurrent_go(proj, ld, q_col, k_col, v_col, nullptr, nullptr, 1.0f, qscale, state, o, seq_slot, seq_start, seqs,
+                            H, dim, vdim, single, dtype, gates, gate_pitch, ones, stream);
 }
 
 // y[t, h, j] = T( o[t, h, j] / sqrt(mean_j o[t, h, :]^2 + eps) * gain[j] * f(g[t, h vdim + j]) ),  f: silu (fn 1) or

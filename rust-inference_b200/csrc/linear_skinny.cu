@@ -87,7 +87,7 @@ template <int NT, typename OutT, bool SWIGLU, int STAGES>
 __global__ void __launch_bounds__(32 * SK_WARPS, STAGES == SK_STAGES ? SK_MIN_BLOCKS : 2)
 linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtensorMap map_w, OutT* __restrict__ y, int M, int N,
                      int K, int early_from, int act, int* __restrict__ err, SkGate gate) {
-    // act (without SWIGLU): 0 nothing, 1 the square of relu, 2 gelu in its tanh form, on the float32 sums before the store
+    // act (without SWIGLU): 0 nothing, 1 the square of relu, 2 gelu in its tanh form, 3 the exact (erf) gelu, on the float32 sums before the store
     extern __shared__ __align__(16) unsigned char sk_raw[];
     SkinnySmem<STAGES>& sm = *reinterpret_cast<SkinnySmem<STAGES>*>(sk_raw + ((1024u - (smem_u32(sk_raw) & 1023u)) & 1023u));
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -226,6 +226,8 @@ linear_skinny_kernel(const bf16* __restrict__ x, const __grid_constant__ CUtenso
                 v *= v;
             } else if (act == 2) {
                 v = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+            } else if (act == 3) {
+                v = 0.5f * v * (1.0f + erff(v * 0.7071067811865476f));
             }
             st_f(y + (size_t)tok * N + n0 + row, v);
         }
@@ -318,11 +320,11 @@ extern "C" int ri_linear_skinny_max_tokens() { return 16; }
 
 // out_f32: 0 = bfloat16 output, 1 = float32 output.  swiglu: 1 = w holds gate and up rows in alternating
 // blocks of 8 and y [M, N/2] gets silu(gate) * up (bfloat16 only).
-// act: an activation on the outputs before they are stored (0 none, 1 relu squared, 2 gelu in its tanh form); not with swiglu.
+// act: an activation on the outputs before they are stored (0 none, 1 relu squared, 2 gelu in its tanh form, 3 the exact gelu); not with swiglu.
 extern "C" int ri_linear_skinny_act(const void* x, const void* w, void* y, int M, int N, int K, int out_f32, int swiglu,
                                     int act, int* err_flag, cudaStream_t stream) {
     if (M == 0 || N == 0) return 0;
-    RI_REQUIRE(act >= 0 && act <= 2 && !(act && swiglu), "linear_skinny: activation %d (with the SiLU gate: %d)", act, swiglu);
+    RI_REQUIRE(act >= 0 && act <= 3 && !(act && swiglu), "linear_skinny: activation %d (with the SiLU gate: %d)", act, swiglu);
     RI_REQUIRE(M > 0 && N > 0 && K > 0, "linear_skinny: bad sizes M=%d N=%d K=%d", M, N, K);
     RI_REQUIRE(M <= 16, "linear_skinny: at most 16 tokens, got %d", M);
     RI_REQUIRE(K % 8 == 0, "linear_skinny: K=%d must be a multiple of 8", K);

@@ -1,8 +1,10 @@
 // A routed feed-forward (mixture of experts): router, plan of the step, grouped products, combination.
 //
-// `moe_route`   per token: logits z = R x (float32), scores s = softmax(z) over all N outputs of the router, choice
-//               scores s + correction, the `top` largest of them (ties: the lower index), and as weights the chosen
-//               outputs' scores s divided by their sum (+ 1e-20).  Every sum has a fixed order.
+// `moe_route`   per token: logits z = R x (float32), scores s = softmax(z) over all N outputs of the router (or the
+//               sigmoid of each), choice scores s + correction, optionally only within the best groups of neighbouring
+//               outputs (`MoeRule`), the `top` largest of them (ties: the lower index), and as weights the chosen
+//               outputs' scores s divided by their sum (+ 1e-20) or as they are, times a constant.  Every sum has a
+//               fixed order.
 // `moe_plan`    the step's (token, choice) pairs grouped by expert: `perm` lists the pairs of expert 0, then of expert
 //               1 and so on (pairs whose choice is not one of the first E outputs, identity experts, are left out), and
 //               `tiles` cuts every expert's run into tiles of MOE_BM rows: (expert, first row in perm, rows).  One
@@ -34,17 +36,128 @@ __device__ __forceinline__ float4 moe_ld4(const bf16* p) {
     return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
 }
 
+// How scores become a choice and weights.  mode 0: scores are the softmax over all outputs; mode 1: the sigmoid of every
+// output on its own.  Choice scores are the scores plus the correction.  groups > 1: the outputs form `groups` equal runs
+// of neighbours, a run's score is the sum of its `gtop` largest choice scores, and only the outputs of the `keep` best
+// runs can be chosen (ties: the lower index, for runs as for outputs).  The weights are the chosen outputs' scores
+// (without the correction) times `scale`, divided by their sum first when `renorm` is set.
+struct MoeRule {
+    int mode, groups, keep, gtop, renorm;
+    float scale;
+};
+
+// One warp: s [N] holds the logits on entry, c [N] and gs [groups] are scratch.
+__device__ __forceinline__ void moe_choose(float* s, float* c, float* gs, const float* __restrict__ correction,
+                                           int* __restrict__ idx, float* __restrict__ weight, int t, int N, int top, int lane,
+                                           const MoeRule rule) {
+    if (rule.mode == 0) {
+        float mx = -INFINITY;
+        for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
+        mx = warp_max(mx);
+        float sum = 0.0f;
+        for (int n = lane; n < N; n += 32) {
+            const float e = expf(s[n] - mx);
+            s[n] = e;
+            sum += e;
+        }
+        sum = warp_sum(sum);
+        for (int n = lane; n < N; n += 32) {
+            s[n] = s[n] / sum;
+            c[n] = s[n] + correction[n];
+        }
+    } else {
+        for (int n = lane; n < N; n += 32) {
+            s[n] = 1.0f / (1.0f + expf(-s[n]));
+            c[n] = s[n] + correction[n];
+        }
+    }
+    __syncwarp();
+    if (rule.groups > 1) {
+        const int size = N / rule.groups;
+        for (int g = lane; g < rule.groups; g += 32) {
+            // the gtop largest of the run, one after the other in the order (value descending, index ascending)
+            float total = 0.0f, last = INFINITY;
+            int last_at = -1;
+            for (int r = 0; r < rule.gtop && r < size; r++) {
+                float best = -INFINITY;
+                int at = -1;
+                for (int n = 0; n < size; n++) {
+                    const float v = c[g * size + n];
+                    const bool after = v < last || (v == last && n > last_at);
+                    if (after && (at < 0 || v > best)) {
+                        best = v;
+                        at = n;
+                    }
+                }
+                if (at < 0) break;
+                total += best;
+                last = best;
+                last_at = at;
+            }
+            gs[g] = total;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            for (int r = 0; r < rule.keep; r++) {
+                float best = -INFINITY;
+                int at = -1;
+                for (int g = 0; g < rule.groups; g++)
+                    if (gs[g] != INFINITY && (at < 0 || gs[g] > best)) {
+                        best = gs[g];
+                        at = g;
+                    }
+                if (at >= 0) gs[at] = INFINITY;           // kept
+            }
+        }
+        __syncwarp();
+        for (int n = lane; n < N; n += 32)
+            if (gs[n / size] != INFINITY) c[n] = -INFINITY;
+        __syncwarp();
+    }
+    float picked_sum = 0.0f;
+    for (int j = 0; j < top; j++) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int n = lane; n < N; n += 32)
+            if (c[n] > best) {                        // ascending n: the first of equals stays
+                best = c[n];
+                at = n;
+            }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) {
+                best = ob;
+                at = oa;
+            }
+        }
+        if (at >= N) at = 0;                           // no finite score left (NaN inputs): still a valid index
+        if (lane == 0) {
+            idx[(size_t)t * top + j] = at;
+            weight[(size_t)t * top + j] = s[at];
+            c[at] = -INFINITY;
+        }
+        picked_sum += s[at];
+        __syncwarp();
+    }
+    if (lane == 0) {
+        const float div = rule.renorm ? picked_sum + 1e-20f : 1.0f;
+        for (int j = 0; j < top; j++) weight[(size_t)t * top + j] = weight[(size_t)t * top + j] / div * rule.scale;
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(32 * MOE_ROUTE_WARPS)
 moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
-                 int* __restrict__ idx, float* __restrict__ weight, int tokens, int D, int N, int top, int vec) {
-    extern __shared__ float moe_sm[];                 // per warp: scores [N], choice scores [N]
+                 int* __restrict__ idx, float* __restrict__ weight, int tokens, int D, int N, int top, int vec, MoeRule rule) {
+    extern __shared__ float moe_sm[];                 // per warp: scores [N], choice scores [N], runs' scores [groups]
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = blockIdx.x * MOE_ROUTE_WARPS + warp;
     if (t >= tokens) return;
-    float* s = moe_sm + (size_t)warp * 2 * N;
+    float* s = moe_sm + (size_t)warp * (2 * N + rule.groups);
     float* c = s + N;
     const T* xr = x + (size_t)t * D;
     for (int n0 = 0; n0 < N; n0 += 4) {
@@ -90,50 +203,7 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
         }
     }
     __syncwarp();
-    float mx = -INFINITY;
-    for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
-    mx = warp_max(mx);
-    float sum = 0.0f;
-    for (int n = lane; n < N; n += 32) {
-        const float e = expf(s[n] - mx);
-        s[n] = e;
-        sum += e;
-    }
-    sum = warp_sum(sum);
-    for (int n = lane; n < N; n += 32) {
-        s[n] = s[n] / sum;
-        c[n] = s[n] + correction[n];
-    }
-    __syncwarp();
-    float picked_sum = 0.0f;
-    for (int j = 0; j < top; j++) {
-        float best = -INFINITY;
-        int at = 0x7fffffff;
-        for (int n = lane; n < N; n += 32)
-            if (c[n] > best) {                        // ascending n: the first of equals stays
-                best = c[n];
-                at = n;
-            }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-            if (ob > best || (ob == best && oa < at)) {
-                best = ob;
-                at = oa;
-            }
-        }
-        if (at >= N) at = 0;                           // no finite score left (NaN inputs): still a valid index
-        if (lane == 0) {
-            idx[(size_t)t * top + j] = at;
-            weight[(size_t)t * top + j] = s[at];
-            c[at] = -INFINITY;
-        }
-        picked_sum += s[at];
-        __syncwarp();
-    }
-    if (lane == 0)
-        for (int j = 0; j < top; j++) weight[(size_t)t * top + j] /= picked_sum + 1e-20f;
+    moe_choose(s, c, c + N, correction, idx, weight, t, N, top, lane, rule);
 }
 
 // The same with a block of 1,024 threads per token, for routers small enough that all their partial sums fit in shared
@@ -145,8 +215,8 @@ moe_route_kernel(const T* __restrict__ x, const float* __restrict__ router, cons
 template <typename T>
 __global__ void __launch_bounds__(MOE_ROUTE_WIDE_THREADS)
 moe_route_wide_kernel(const T* __restrict__ x, const float* __restrict__ router, const float* __restrict__ correction,
-                      int* __restrict__ idx, float* __restrict__ weight, int D, int N, int top) {
-    extern __shared__ float moe_sm[];                 // partial sums [N][segs], scores [N], choice scores [N]
+                      int* __restrict__ idx, float* __restrict__ weight, int D, int N, int top, MoeRule rule) {
+    extern __shared__ float moe_sm[];                 // partial sums [N][segs], scores [N], choice scores [N], runs' scores
     pdl_trigger();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -177,71 +247,35 @@ moe_route_wide_kernel(const T* __restrict__ x, const float* __restrict__ router,
     }
     __syncthreads();
     if (warp > 0) return;
-    float mx = -INFINITY;
-    for (int n = lane; n < N; n += 32) mx = fmaxf(mx, s[n]);
-    mx = warp_max(mx);
-    float sum = 0.0f;
-    for (int n = lane; n < N; n += 32) {
-        const float e = expf(s[n] - mx);
-        s[n] = e;
-        sum += e;
-    }
-    sum = warp_sum(sum);
-    for (int n = lane; n < N; n += 32) {
-        s[n] = s[n] / sum;
-        c[n] = s[n] + correction[n];
-    }
-    __syncwarp();
-    float picked_sum = 0.0f;
-    for (int j = 0; j < top; j++) {
-        float best = -INFINITY;
-        int at = 0x7fffffff;
-        for (int n = lane; n < N; n += 32)
-            if (c[n] > best) {
-                best = c[n];
-                at = n;
-            }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
-            if (ob > best || (ob == best && oa < at)) {
-                best = ob;
-                at = oa;
-            }
-        }
-        if (at >= N) at = 0;
-        if (lane == 0) {
-            idx[(size_t)t * top + j] = at;
-            weight[(size_t)t * top + j] = s[at];
-            c[at] = -INFINITY;
-        }
-        picked_sum += s[at];
-        __syncwarp();
-    }
-    if (lane == 0)
-        for (int j = 0; j < top; j++) weight[(size_t)t * top + j] /= picked_sum + 1e-20f;
+    moe_choose(s, c, c + N, correction, idx, weight, t, N, top, lane, rule);
 }
 
-extern "C" int ri_moe_route(const void* x, const float* router, const float* correction, int* idx, float* weight,
-                            int tokens, int D, int N, int top, int dtype, cudaStream_t stream) {
+extern "C" int ri_moe_route_rule(const void* x, const float* router, const float* correction, int* idx, float* weight,
+                                 int tokens, int D, int N, int top, int mode, int groups, int keep, int gtop, float scale,
+                                 int renorm, int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
+    RI_REQUIRE(mode == 0 || mode == 1, "moe_route: score rule %d", mode);
+    RI_REQUIRE(groups >= 1 && N % groups == 0 && keep >= 1 && keep <= groups && gtop >= 1,
+               "moe_route: %d outputs in %d groups of which %d are kept", N, groups, keep);
+    RI_REQUIRE(top <= keep * (N / groups), "moe_route: top %d of the %d outputs of the kept groups", top, keep * (N / groups));
+    MoeRule rule;
+    rule.mode = mode; rule.groups = groups; rule.keep = keep; rule.gtop = gtop; rule.renorm = renorm; rule.scale = scale;
     RI_REQUIRE(tokens > 0 && D > 0 && N > 0 && top > 0 && top <= N, "moe_route: bad sizes (top %d of %d)", top, N);
     RI_REQUIRE(N <= 4096, "moe_route: %d router outputs (up to 4096 are built)", N);
-    const size_t smem = (size_t)MOE_ROUTE_WARPS * 2 * N * sizeof(float);
+    const size_t smem = (size_t)MOE_ROUTE_WARPS * (2 * N + groups) * sizeof(float);
     const dim3 grid((tokens + MOE_ROUTE_WARPS - 1) / MOE_ROUTE_WARPS);
     // (which form runs depends on the sizes and addresses only, never on the batch)
     const int vec = (D % 4 == 0 && (((uintptr_t)router | (uintptr_t)x) & 15) == 0) ? 1 : 0;
     cudaError_t e = cudaSuccess;
     const long long items = (long long)N * ((D + 127) / 128);
     if (vec && items <= MOE_ROUTE_WIDE_ITEMS && tokens <= 65535 * 32) {
-        const size_t sm = (size_t)(items + 2 * N) * sizeof(float);
+        const size_t sm = (size_t)(items + 2 * N + groups) * sizeof(float);
         if (dtype == RI_DTYPE_F32)
             ri_launch_pdl(moe_route_wide_kernel<float>, dim3(tokens), dim3(MOE_ROUTE_WIDE_THREADS), sm, stream, (const float*)x,
-                          router, correction, idx, weight, D, N, top);
+                          router, correction, idx, weight, D, N, top, rule);
         else if (dtype == RI_DTYPE_BF16)
             ri_launch_pdl(moe_route_wide_kernel<bf16>, dim3(tokens), dim3(MOE_ROUTE_WIDE_THREADS), sm, stream, (const bf16*)x,
-                          router, correction, idx, weight, D, N, top);
+                          router, correction, idx, weight, D, N, top, rule);
         else RI_FAIL(-1, "moe_route: unknown dtype %d", dtype);
         RI_CHECK_LAUNCH("moe_route");
         return 0;
@@ -250,12 +284,12 @@ extern "C" int ri_moe_route(const void* x, const float* router, const float* cor
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RI_FAIL((int)e, "moe_route: %s", cudaGetErrorString(e));
         ri_launch_pdl(moe_route_kernel<float>, grid, dim3(32 * MOE_ROUTE_WARPS), smem, stream, (const float*)x, router,
-                      correction, idx, weight, tokens, D, N, top, vec);
+                      correction, idx, weight, tokens, D, N, top, vec, rule);
     } else if (dtype == RI_DTYPE_BF16) {
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) RI_FAIL((int)e, "moe_route: %s", cudaGetErrorString(e));
         ri_launch_pdl(moe_route_kernel<bf16>, grid, dim3(32 * MOE_ROUTE_WARPS), smem, stream, (const bf16*)x, router,
-                      correction, idx, weight, tokens, D, N, top, vec);
+                      correction, idx, weight, tokens, D, N, top, vec, rule);
     } else RI_FAIL(-1, "moe_route: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("moe_route");
     return 0;
@@ -659,4 +693,9 @@ extern "C" int ri_moe_combine(const float* pair_out, const int* idx, const float
     else RI_FAIL(-1, "moe_combine: unknown dtype %d", dtype);
     RI_CHECK_LAUNCH("moe_combine");
     return 0;
+}
+
+extern "C" int ri_moe_route(const void* x, const float* router, const float* correction, int* idx, float* weight,
+                            int tokens, int D, int N, int top, int dtype, cudaStream_t stream) {
+    return ri_moe_route_rule(x, router, correction, idx, weight, tokens, D, N, top, 0, 1, 1, 1, 1.0f, 1, dtype, stream);
 }

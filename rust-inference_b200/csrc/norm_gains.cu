@@ -4,10 +4,14 @@
 // resid [n, dim] float32.  One block per output row does, element by element and in this order:
 //   1. the outputs that the layer before left pending (compute type T, up to two, each with an optional float32
 //      factor w[0]):  one output  x' = x + w1 y1;  two  x' = x + (w1 y1 + w2 y2)   (the outputs' sum first);
+//      with a norm behind the sublayer (`post_gain`, float32 [dim]) the sum s = w1 y1 (+ w2 y2) is normed before it
+//      joins:  x' = x + s / sqrt(mean(s^2) + post_eps) * post_gain   (the gain holds the layer's scale as well);
 //   2. the terms of a pass's entry: x' += float(table[ids[row]]) * scale   (the embedding's row once more; ids null: not),
 //      then x' += vec   (a learned vector; null: not);
 //      x' is written back to resid, unless only some rows are read (`rows`: nothing reads resid after that call);
 //   3. r = 1 / sqrt(mean(x'^2) + eps);  out1 = x' r gain1  and, with a second gain, out2 = x' r gain2.
+//      Without gain1 nothing is normed: out1 (if given) gets x' itself in the compute type, its rows `out_pitch`
+//      elements apart (the left half of a wider matrix that a product reads next).
 // A layer whose mixer and feed-forward both read the same residual, each through a norm of its own, needs the
 // statistic once and the residual read once; that is what the second gain is for.
 // All arithmetic is float32 whatever T is.  The block size and the order of a row's additions depend on dim (and on
@@ -39,6 +43,9 @@ struct NgArgs {
     int dim, vocab, write_back;
     float scale, eps;
     int* err;
+    const float* post_gain;
+    float post_eps;
+    long long out_pitch;
     int n_rows;          // blocks past the rows ask for the weights that the linear after this norm reads first
     WeightHint next;
 };
@@ -83,17 +90,51 @@ __global__ void __launch_bounds__(512) norm_gains_kernel(NgArgs a) {
     const T* y1 = a.y1 ? (const T*)a.y1 + r * dim : nullptr;
     const T* y2 = (a.y1 && a.y2) ? (const T*)a.y2 + r * dim : nullptr;
     const bool changes = y1 || trow || a.vec;
+    const bool post = y1 && a.post_gain;
     float sum = 0.0f;
+    float pinv = 1.0f;
+    if (post) {
+        // the pending outputs' sum, normed on its own before it joins: the sum waits in the row buffer
+        float ss = 0.0f;
+        if (VEC) {
+            for (int i = threadIdx.x; i < (dim >> 2); i += blockDim.x) {
+                const float4 p1 = ng_ld4(y1 + 4 * i);
+                float4 s4 = make_float4(w1 * p1.x, w1 * p1.y, w1 * p1.z, w1 * p1.w);
+                if (y2) {
+                    const float4 p2 = ng_ld4(y2 + 4 * i);
+                    s4 = make_float4(s4.x + w2 * p2.x, s4.y + w2 * p2.y, s4.z + w2 * p2.z, s4.w + w2 * p2.w);
+                }
+                *reinterpret_cast<float4*>(ng_row + 4 * i) = s4;
+                ss += (s4.x * s4.x + s4.y * s4.y) + (s4.z * s4.z + s4.w * s4.w);
+            }
+        } else {
+            for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+                float v = w1 * ld_f(y1 + i);
+                if (y2) v = v + w2 * ld_f(y2 + i);
+                ng_row[i] = v;
+                ss += v * v;
+            }
+        }
+        pinv = 1.0f / sqrtf(block_sum(ss, red) / (float)dim + a.post_eps);
+    }
     if (VEC) {
         for (int i = threadIdx.x; i < (dim >> 2); i += blockDim.x) {
             float4 x = ng_ld4(rp + 4 * i);
             if (changes) {
                 float4 p1 = make_float4(0.f, 0.f, 0.f, 0.f), p2 = p1, tr = p1, vv = p1;
-                if (y1) p1 = ng_ld4(y1 + 4 * i);
-                if (y2) p2 = ng_ld4(y2 + 4 * i);
+                if (post) {
+                    const float4 s4 = *reinterpret_cast<const float4*>(ng_row + 4 * i);
+                    const float4 pg = ng_ld4(a.post_gain + 4 * i);
+                    x.x = x.x + s4.x * pinv * pg.x; x.y = x.y + s4.y * pinv * pg.y;
+                    x.z = x.z + s4.z * pinv * pg.z; x.w = x.w + s4.w * pinv * pg.w;
+                } else {
+                    if (y1) p1 = ng_ld4(y1 + 4 * i);
+                    if (y2) p2 = ng_ld4(y2 + 4 * i);
+                }
                 if (trow) tr = ng_ld4(trow + 4 * i);
                 if (a.vec) vv = ng_ld4(a.vec + 4 * i);
-                if (y2) {
+                if (post) {
+                } else if (y2) {
                     x.x = x.x + (w1 * p1.x + w2 * p2.x); x.y = x.y + (w1 * p1.y + w2 * p2.y);
                     x.z = x.z + (w1 * p1.z + w2 * p2.z); x.w = x.w + (w1 * p1.w + w2 * p2.w);
                 } else if (y1) {
@@ -110,12 +151,26 @@ __global__ void __launch_bounds__(512) norm_gains_kernel(NgArgs a) {
         for (int i = threadIdx.x; i < dim; i += blockDim.x) {
             float x = rp[i];
             if (changes) {
-                x = ng_join<T>(x, y1, y2, w1, w2, trow, a.scale, a.vec, i);
+                if (post) {
+                    x = x + ng_row[i] * pinv * a.post_gain[i];
+                    x = ng_join<T>(x, nullptr, nullptr, w1, w2, trow, a.scale, a.vec, i);
+                } else {
+                    x = ng_join<T>(x, y1, y2, w1, w2, trow, a.scale, a.vec, i);
+                }
                 if (a.write_back) rp[i] = x;
             }
             ng_row[i] = x;
             sum += x * x;
         }
+    }
+    if (!a.gain1) {
+        // nothing is normed: the new residual itself, in the compute type, for whoever reads it next
+        if (a.out1) {
+            __syncthreads();
+            T* oc = (T*)a.out1 + (size_t)blockIdx.x * a.out_pitch;
+            for (int i = threadIdx.x; i < dim; i += blockDim.x) st_f(oc + i, ng_row[i]);
+        }
+        return;
     }
     const float inv = 1.0f / sqrtf(block_sum(sum, red) / (float)dim + a.eps);
     T* o1 = (T*)a.out1 + (size_t)blockIdx.x * dim;
@@ -147,12 +202,23 @@ __global__ void __launch_bounds__(512) norm_gains_kernel(NgArgs a) {
 extern "C" int ri_norm_gains(float* resid, const void* y1, const float* w1, const void* y2, const float* w2, const int* ids,
                              const void* table, int vocab, float scale, const float* vec, const int* rows,
                              const float* gain1, const float* gain2, void* out1, void* out2, int n_rows, int dim, float eps,
-                             int dtype, const void* next_w, int next_n, int next_k, int* err_flag, cudaStream_t stream) {
+                             int dtype, const void* next_w, int next_n, int next_k, int* err_flag, cudaStream_t stream);
+
+// The same with a norm behind the pending outputs (post_gain [dim] float32 or null, post_eps) and, when gain1 is null,
+// no norm in front: out1 (or null) then gets the new residual in the compute type at rows `out_pitch` elements apart.
+extern "C" int ri_norm_gains_post(float* resid, const void* y1, const float* w1, const void* y2, const float* w2, const int* ids,
+                                  const void* table, int vocab, float scale, const float* vec, const int* rows,
+                                  const float* gain1, const float* gain2, void* out1, void* out2, int n_rows, int dim,
+                                  float eps, const float* post_gain, float post_eps, long long out_pitch, int dtype,
+                                  const void* next_w, int next_n, int next_k, int* err_flag, cudaStream_t stream) {
     if (n_rows == 0) return 0;
     RI_REQUIRE(n_rows > 0 && dim > 0, "norm_gains: bad sizes rows=%d dim=%d", n_rows, dim);
     RI_REQUIRE(dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16, "norm_gains: unknown dtype %d", dtype);
     RI_REQUIRE(y1 || !y2, "norm_gains: pending outputs are given first, second");
     RI_REQUIRE((gain2 == nullptr) == (out2 == nullptr), "norm_gains: a second gain and a second output go together");
+    RI_REQUIRE(gain1 || (!gain2 && !next_w), "norm_gains: without a first gain nothing is normed");
+    RI_REQUIRE(gain1 ? out1 != nullptr : (!out1 || out_pitch >= dim), "norm_gains: bad output for %d columns", dim);
+    RI_REQUIRE(!post_gain || y1, "norm_gains: a norm behind the sublayer needs its output");
     RI_REQUIRE(!ids || (table && vocab > 0), "norm_gains: token ids need the table");
     RI_REQUIRE(!ids || !rows, "norm_gains: the entry terms join whole steps, not selected rows");
     const size_t smem = (size_t)dim * sizeof(float);
@@ -161,6 +227,7 @@ extern "C" int ri_norm_gains(float* resid, const void* y1, const float* w1, cons
     a.resid = resid; a.y1 = y1; a.y2 = y2; a.table = ids ? table : nullptr; a.w1 = w1; a.w2 = w2; a.vec = vec;
     a.gain1 = gain1; a.gain2 = gain2; a.ids = ids; a.rows = rows; a.out1 = out1; a.out2 = out2; a.dim = dim; a.vocab = vocab;
     a.write_back = rows ? 0 : 1; a.scale = scale; a.eps = eps; a.err = err_flag;
+    a.post_gain = post_gain; a.post_eps = post_eps; a.out_pitch = out_pitch;
     a.n_rows = n_rows;
     a.next = make_weight_hint(nullptr, 0, 0, 0);
     if (next_w) {
@@ -173,7 +240,7 @@ extern "C" int ri_norm_gains(float* resid, const void* y1, const float* w1, cons
         a.next = make_weight_hint(next_w, next_n, next_k, sms);
     }
     const uintptr_t unit = dtype == RI_DTYPE_F32 ? 15 : 7;
-    const bool vec4 = dim % 4 == 0 && (((uintptr_t)resid | (uintptr_t)gain1 | (uintptr_t)gain2 | (uintptr_t)vec) & 15) == 0 &&
+    const bool vec4 = dim % 4 == 0 && (((uintptr_t)resid | (uintptr_t)gain1 | (uintptr_t)gain2 | (uintptr_t)vec | (uintptr_t)post_gain) & 15) == 0 &&
                       (((uintptr_t)y1 | (uintptr_t)y2 | (uintptr_t)table | (uintptr_t)out1 | (uintptr_t)out2) & unit) == 0;
     // by the row length alone: the order of a row's additions must not depend on how many rows the step has
     int threads;
@@ -206,4 +273,12 @@ extern "C" int ri_norm_gains(float* resid, const void* y1, const float* w1, cons
 #undef NG_GO
     RI_CHECK_LAUNCH("norm_gains");
     return 0;
+}
+
+extern "C" int ri_norm_gains(float* resid, const void* y1, const float* w1, const void* y2, const float* w2, const int* ids,
+                             const void* table, int vocab, float scale, const float* vec, const int* rows,
+                             const float* gain1, const float* gain2, void* out1, void* out2, int n_rows, int dim, float eps,
+                             int dtype, const void* next_w, int next_n, int next_k, int* err_flag, cudaStream_t stream) {
+    return ri_norm_gains_post(resid, y1, w1, y2, w2, ids, table, vocab, scale, vec, rows, gain1, gain2, out1, out2, n_rows, dim,
+                              eps, nullptr, 0.0f, 0, dtype, next_w, next_n, next_k, err_flag, stream);
 }

@@ -7,7 +7,10 @@
 //   bias [..]:         float32, indexed by the product's column (null: none); added first
 //   q_out [tokens, H, Dp];  k_pool, v_pool [pages, KV, page_size, Dp]
 //
-// For a q or k head x (after the bias): the first `rot` elements are turned by the angles of the token's position,
+// For a q or k head x (after the bias), with `norm` 1: x <- x / sqrt(sum(x^2) / Dk + norm_eps) * gain (q_gain, k_gain:
+// float32 [Dp], the same for every head); with `norm` 2 the sum runs over ALL q heads (all k heads) of the token at once,
+//     x <- x / sqrt(sum over the heads of sum(x^2) / (H Dk) + norm_eps) * gain[h],   gains [H, Dp] and [KV, Dp],
+// both before the rotation.  Then the first `rot` elements are turned by the angles of the token's position,
 // (c, s) = table[pos][i]: partners are neighbours (2i, 2i+1) with `pairs`, else i and i + rot/2:
 //     a' = a c - b s,  b' = b c + a s;
 // then, with `unit`, the head is divided by its root mean square over its Dk true elements:
@@ -28,6 +31,9 @@ struct QpArgs {
     const float2* rope;
     int rope_rows, rot, pairs, unit;
     float eps;
+    const float *q_gain, *k_gain;
+    int norm;
+    float norm_eps;
     int H, KV, Dp, Dk, mpps, page_size, num_pages, write_kv;
     int* err;
 };
@@ -44,10 +50,30 @@ __device__ __forceinline__ int qp_page(const QpArgs& a, int t, int pos) {
     return page;
 }
 
+// norm 2: 1 / sqrt(mean of the squares over all q heads' (k heads') true elements + eps), by the whole block, in a
+// fixed order; padding columns hold zeros (a zero row of the matrix and a zero of the bias) and add nothing
+template <typename T>
+__device__ __forceinline__ void qp_whole_norms(const QpArgs& a, const T* row, float* red, float& inv_q, float& inv_k) {
+    float sq = 0.0f, sk = 0.0f;
+    for (int c = threadIdx.x; c < a.H * a.Dp; c += blockDim.x) {
+        const float v = ld_f(row + a.q_col + c) + (a.bias ? a.bias[a.q_col + c] : 0.0f);
+        sq += v * v;
+    }
+    for (int c = threadIdx.x; c < a.KV * a.Dp; c += blockDim.x) {
+        const float v = ld_f(row + a.k_col + c) + (a.bias ? a.bias[a.k_col + c] : 0.0f);
+        sk += v * v;
+    }
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    inv_q = a.H ? 1.0f / sqrtf(sq / (float)(a.H * a.Dk) + a.norm_eps) : 1.0f;
+    inv_k = a.KV ? 1.0f / sqrtf(sk / (float)(a.KV * a.Dk) + a.norm_eps) : 1.0f;
+}
+
 // any sizes: a warp per head, lanes strided over the head, the head staged in shared memory
 template <typename T>
 __global__ void qkv_prep_kernel(QpArgs a) {
     __shared__ float buf[QP_WARPS][QP_MAX_DP];
+    __shared__ float red[33];
     pdl_trigger();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -64,6 +90,8 @@ __global__ void qkv_prep_kernel(QpArgs a) {
     const int half = a.rot / 2;
     const T* row = (const T*)a.proj + (size_t)t * a.ld;
     float* x = buf[warp];
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (a.norm == 2) qp_whole_norms<T>(a, row, red, inv_q, inv_k);
     for (int h = blockIdx.y * QP_WARPS + warp; h < heads_total; h += QP_WARPS * gridDim.y) {
         const int which = h < H ? 0 : (h < H + KV ? 1 : 2);
         const int hh = which == 0 ? h : (which == 1 ? h - H : h - H - KV);
@@ -81,6 +109,19 @@ __global__ void qkv_prep_kernel(QpArgs a) {
             for (int d = lane; d < Dp; d += 32) st_f(dst + d, x[d]);
             __syncwarp();
             continue;
+        }
+        if (a.norm) {
+            const float* gain = which == 0 ? a.q_gain : a.k_gain;
+            float ninv = which == 0 ? inv_q : inv_k;
+            if (a.norm == 1) {
+                float ss = 0.0f;
+                for (int d = lane; d < Dp; d += 32) ss += x[d] * x[d];
+                ninv = 1.0f / sqrtf(warp_sum(ss) / (float)a.Dk + a.norm_eps);
+            } else {
+                gain += (size_t)hh * Dp;
+            }
+            for (int d = lane; d < Dp; d += 32) x[d] = x[d] * ninv * gain[d];
+            __syncwarp();
         }
         if (a.rope) {
             const float2* cs = a.rope + (size_t)pos * half;
@@ -142,8 +183,11 @@ template <> struct Qp8<__nv_bfloat16> {
     }
 };
 
+// Partners half a rotated part apart (`pairs` 0) live in another lane of the head's group, rot / 16 lanes away (rot is
+// then a multiple of 16, so that a lane's eight elements lie on one side); a lane fetches them by shuffles.
 template <typename T>
 __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
+    __shared__ float red[33];
     pdl_trigger();
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -161,11 +205,34 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
     for (int j = 0; j < 4; j++) {
         cs_c[j] = 1.0f;
         cs_s[j] = 0.0f;
-        if (a.rope && rope_ok && live_lane && d0 + 2 * j < a.rot) {
+        if (a.rope && a.pairs && rope_ok && live_lane && d0 + 2 * j < a.rot) {
             const float2 c = a.rope[(size_t)pos * (a.rot / 2) + d0 / 2 + j];
             cs_c[j] = c.x;
             cs_s[j] = c.y;
         }
+    }
+    // halves: this lane's eight angles, the side it is on (the sine's sign) and how far away its partners are
+    const int half = a.rot / 2;
+    const bool turns = a.rope && !a.pairs && live_lane && d0 < a.rot;
+    const bool upper = d0 >= half;
+    float hc[8], hs[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        hc[j] = 1.0f;
+        hs[j] = 0.0f;
+        if (turns && rope_ok) {
+            const float2 c = a.rope[(size_t)pos * half + (upper ? d0 - half : d0) + j];
+            hc[j] = c.x;
+            hs[j] = upper ? c.y : -c.y;
+        }
+    }
+    const int partner = turns ? (upper ? lane - half / 8 : lane + half / 8) : lane;
+    float gq[8], gk[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) gq[j] = gk[j] = 1.0f;
+    if (a.norm == 1 && live_lane) {
+        if (a.q_gain) Qp8<float>::load(a.q_gain + d0, gq);
+        if (a.k_gain) Qp8<float>::load(a.k_gain + d0, gk);
     }
     pdl_wait();
     if (!rope_ok) {
@@ -174,6 +241,8 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
     }
     const int heads_total = H + KV + (a.v_col >= 0 ? KV : 0);
     const T* row = (const T*)a.proj + (size_t)t * a.ld;
+    float inv_q = 1.0f, inv_k = 1.0f;
+    if (a.norm == 2) qp_whole_norms<T>(a, row, red, inv_q, inv_k);
     const int stride = QP_WARPS * hpw * gridDim.y;
     for (int h0 = (blockIdx.y * QP_WARPS + warp) * hpw; h0 < heads_total; h0 += stride) {
         const int h = h0 + sub;
@@ -196,7 +265,35 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
             else if (page >= 0)
                 dst = (T*)(which == 1 ? a.k_pool : a.v_pool) + (((size_t)page * KV + hh) * a.page_size + pos % a.page_size) * Dp + d0;
         }
-        if (which < 2) {
+        if (a.norm) {
+            float ninv = which == 0 ? inv_q : inv_k;
+            if (a.norm == 1) {
+                float ss = 0.0f;
+#pragma unroll
+                for (int j = 0; j < 8; j++) ss += x[j] * x[j];
+                for (int o = group >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                ninv = 1.0f / sqrtf(ss / (float)a.Dk + a.norm_eps);
+            }
+            if (which < 2) {
+                float g8[8];
+                if (a.norm == 2) {
+                    Qp8<float>::load((which == 0 ? a.q_gain : a.k_gain) + (size_t)hh * Dp + d0, g8);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 8; j++) g8[j] = which == 0 ? gq[j] : gk[j];
+                }
+#pragma unroll
+                for (int j = 0; j < 8; j++) x[j] = x[j] * ninv * g8[j];
+            }
+        }
+        if (a.rope && !a.pairs) {
+            // every lane takes part in the shuffles; a lane that does not turn keeps its own values (cos 1, sin 0)
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float other = __shfl_sync(0xffffffffu, x[j], partner);
+                if (which < 2) x[j] = x[j] * hc[j] + other * hs[j];
+            }
+        } else if (which < 2) {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
                 const float u = x[2 * j], v = x[2 * j + 1];
@@ -223,8 +320,19 @@ extern "C" int ri_qkv_prep(const void* proj, long long ld, int q_col, int k_col,
                            void* k_pool, void* v_pool, const int* page_table, const int* tok_seq, const int* tok_pos,
                            const int* seq_slot, const float* rope_table, int rope_rows, int rot, int pairs, int unit,
                            float eps, int tokens, int H, int KV, int Dp, int Dk, int mpps, int page_size, int num_pages,
-                           int write_kv, int dtype, int* err_flag, cudaStream_t stream) {
+                           int write_kv, int dtype, int* err_flag, cudaStream_t stream);
+
+// The same with a norm of q and k heads before the rotation: norm 1 per head (gains [Dp]), 2 over all heads of the
+// token at once (gains [H, Dp] and [KV, Dp]); 0: none.
+extern "C" int ri_qkv_prep_norm(const void* proj, long long ld, int q_col, int k_col, int v_col, const float* bias, void* q_out,
+                                void* k_pool, void* v_pool, const int* page_table, const int* tok_seq, const int* tok_pos,
+                                const int* seq_slot, const float* rope_table, int rope_rows, int rot, int pairs, int unit,
+                                float eps, const float* q_gain, const float* k_gain, int norm, float norm_eps, int tokens,
+                                int H, int KV, int Dp, int Dk, int mpps, int page_size, int num_pages, int write_kv,
+                                int dtype, int* err_flag, cudaStream_t stream) {
     if (tokens == 0) return 0;
+    RI_REQUIRE(norm >= 0 && norm <= 2, "qkv_prep: norm %d", norm);
+    RI_REQUIRE(!norm || ((q_gain || !H) && (k_gain || !KV)), "qkv_prep: a norm needs its gains");
     RI_REQUIRE(tokens > 0 && H >= 0 && KV >= 0 && H + KV > 0 && Dp > 0 && Dk > 0 && Dk <= Dp, "qkv_prep: bad sizes");
     RI_REQUIRE(Dp <= QP_MAX_DP, "qkv_prep: heads of %d elements exceed the limit %d", Dp, QP_MAX_DP);
     RI_REQUIRE(rot >= 0 && rot <= Dk && rot % 2 == 0, "qkv_prep: %d rotated elements must be even and within the head's %d", rot, Dk);
@@ -236,20 +344,23 @@ extern "C" int ri_qkv_prep(const void* proj, long long ld, int q_col, int k_col,
     a.proj = proj; a.ld = ld; a.q_col = q_col; a.k_col = k_col; a.v_col = v_col; a.bias = bias; a.q_out = q_out;
     a.k_pool = k_pool; a.v_pool = v_pool; a.page_table = page_table; a.tok_seq = tok_seq; a.tok_pos = tok_pos;
     a.seq_slot = seq_slot; a.rope = (const float2*)rope_table; a.rope_rows = rope_rows; a.rot = rope_table ? rot : 0;
+    a.q_gain = q_gain; a.k_gain = k_gain; a.norm = norm; a.norm_eps = norm_eps;
     a.pairs = pairs; a.unit = unit; a.eps = eps; a.H = H; a.KV = KV; a.Dp = Dp; a.Dk = Dk; a.mpps = mpps;
     a.page_size = page_size; a.num_pages = num_pages; a.write_kv = write_kv; a.err = err_flag;
     const int heads_total = H + KV + (v_col >= 0 ? KV : 0);
     const int es = dtype == RI_DTYPE_F32 ? 4 : 2;
     // every piece of eight elements must start on 16 bytes: the row pitch, the columns, the heads and the pointers
-    const bool vec = Dp % 8 == 0 && Dp <= 256 && (pairs || !rope_table) && (ld * es) % 16 == 0 && (q_col * es) % 16 == 0 &&
-                     (k_col * es) % 16 == 0 && (v_col < 0 || (v_col * es) % 16 == 0) &&
-                     ((((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)bias) & 15) == 0);
+    const bool vec = Dp % 8 == 0 && Dp <= 256 && (pairs || !rope_table || rot % 16 == 0) && (ld * es) % 16 == 0 &&
+                     (q_col * es) % 16 == 0 && (k_col * es) % 16 == 0 && (v_col < 0 || (v_col * es) % 16 == 0) &&
+                     ((((uintptr_t)proj | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)bias |
+                        (uintptr_t)q_gain | (uintptr_t)k_gain) & 15) == 0);
     if (vec) {
         int group = 1;
         while (group < Dp / 8) group <<= 1;
         const int per_block = QP_WARPS * (32 / group);
         int hb = (heads_total + per_block - 1) / per_block;
         if ((long long)tokens * hb > 4096) hb = 1 > 4096 / tokens ? 1 : 4096 / tokens;
+        if (norm == 2) hb = 1;                      // the block adds up the token's whole projection once
         RI_REQUIRE(hb <= 65535, "qkv_prep: bad grid");
         dim3 grid(tokens, hb);
         if (dtype == RI_DTYPE_F32) ri_launch_pdl(qkv_prep_vec_kernel<float>, grid, dim3(32 * QP_WARPS), 0, stream, a, group);
@@ -259,10 +370,21 @@ extern "C" int ri_qkv_prep(const void* proj, long long ld, int q_col, int k_col,
     }
     int hb = (heads_total + QP_WARPS - 1) / QP_WARPS;
     if ((long long)tokens * hb > 4096) hb = 1 > 4096 / tokens ? 1 : 4096 / tokens;
+    if (norm == 2) hb = 1;
     RI_REQUIRE(hb <= 65535, "qkv_prep: bad grid");
     dim3 grid(tokens, hb);
     if (dtype == RI_DTYPE_F32) ri_launch_pdl(qkv_prep_kernel<float>, grid, dim3(32 * QP_WARPS), 0, stream, a);
     else ri_launch_pdl(qkv_prep_kernel<__nv_bfloat16>, grid, dim3(32 * QP_WARPS), 0, stream, a);
     RI_CHECK_LAUNCH("qkv_prep");
     return 0;
+}
+
+extern "C" int ri_qkv_prep(const void* proj, long long ld, int q_col, int k_col, int v_col, const float* bias, void* q_out,
+                           void* k_pool, void* v_pool, const int* page_table, const int* tok_seq, const int* tok_pos,
+                           const int* seq_slot, const float* rope_table, int rope_rows, int rot, int pairs, int unit,
+                           float eps, int tokens, int H, int KV, int Dp, int Dk, int mpps, int page_size, int num_pages,
+                           int write_kv, int dtype, int* err_flag, cudaStream_t stream) {
+    return ri_qkv_prep_norm(proj, ld, q_col, k_col, v_col, bias, q_out, k_pool, v_pool, page_table, tok_seq, tok_pos, seq_slot,
+                            rope_table, rope_rows, rot, pairs, unit, eps, nullptr, nullptr, 0, 0.0f, tokens, H, KV, Dp, Dk,
+                            mpps, page_size, num_pages, write_kv, dtype, err_flag, stream);
 }

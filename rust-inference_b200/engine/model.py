@@ -210,7 +210,7 @@ class Model:
         delta = None
         for e in self.spec.schedule:
             if e.enters >= 0:
-                delta = self.pass_entry(delta, e.enters, ids)
+                resid, delta = self.pass_entry.enter(resid, delta, e.enters, ids)
             resid, delta = self.blocks[e.layer](resid, delta, ctx, cache.layer(e.cache, e.writes))
         if self.final_norm.takes_hint:
             x = self.final_norm(resid, delta, want_rows, self.head_part.reads_first())

@@ -25,6 +25,13 @@ _SIGNATURES = {
     ("elementwise", "ri_embed_rows"): [_P, _P, _P, _I, _I, _I, _I, _P, _P],
     ("elementwise", "ri_embed_rows_scaled"): [_P, _P, _P, _I, _I, _I, _F, _I, _I, _P, _P],
     ("elementwise", "ri_activation"): [_P, _P, _L, _I, _I, _P],
+    ("elementwise", "ri_embed_rows_same"): [_P, _P, _P, _L, _I, _I, _I, _I, _P, _P],
+    ("norm_gains", "ri_norm_gains_post"): [_P] * 6 + [_P, _I, _F] + [_P] * 6 + [_I, _I, _F, _P, _F, _L, _I, _P, _I, _I, _P, _P],
+    ("qkv_prep", "ri_qkv_prep_norm"): [_P, _L, _I, _I, _I] + [_P] * 9 + [_I, _I, _I, _I, _F, _P, _P, _I, _F] + [_I] * 10 + [_P, _P],
+    ("moe", "ri_moe_route_rule"): [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
+    ("gla", "ri_gla_recurrent_scalar"): [_P, _L, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
+    ("mlstm", "ri_mlstm_gates"): [_P, _L, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _P],
+    ("mlstm", "ri_mlstm_head_norm_gate"): [_P, _P, _P, _F, _P, _L, _P, _I, _I, _I, _I, _I, _P],
     ("elementwise", "ri_gate_heads"): [_P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     ("streams", "ri_stream_norm"): [_P] * 8 + [_I, _I, _I, _F, _I, _I, _P],
     ("streams", "ri_stream_norm2"): [_P] * 13 + [_I, _I, _I, _F, _I, _I, _P],
@@ -270,11 +277,12 @@ def stream_norm(resid: torch.Tensor, gain: torch.Tensor, eps: float, out_dtype: 
     return out
 
 
-ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1}
+ACTIVATIONS = {"relu2": 0, "gelu_tanh": 1, "gelu": 2}
 
 
 def activation(x: torch.Tensor, kind: str) -> torch.Tensor:
-    """Element by element: "relu2" relu(x)^2, "gelu_tanh" 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))."""
+    """Element by element: "relu2" relu(x)^2, "gelu_tanh" 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), "gelu" the
+    exact form 0.5 x (1 + erf(x / sqrt(2)))."""
     _need(x, "x")
     if kind not in ACTIVATIONS:
         raise KernelError(f"activation {kind!r} is not built (known: {', '.join(sorted(ACTIVATIONS))})")
@@ -417,6 +425,81 @@ def head_norm_gate(o: torch.Tensor, gain: torch.Tensor, eps: float, g: torch.Ten
     y = torch.empty((tokens, H * width), dtype=out_dtype, device=o.device)
     _call("gla", "ri_gla_head_norm_gate", o.data_ptr(), gain.data_ptr(), float(eps), g.data_ptr(), ldg, y.data_ptr(), tokens,
           H, width, {"sigmoid": 0, "silu": 1}[fn], _code(out_dtype), _stream())
+    return y
+
+
+def mlstm_gates(proj: torch.Tensor, i_col: int, f_col: int, i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float,
+                m_state: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, heads: int) -> torch.Tensor:
+    """The gates of the matrix memory for the step's new tokens.  ``proj`` [tokens, N] holds the input gate's
+    pre-activation of head h at column ``i_col`` + h and the forget gate's at ``f_col`` + h.  With
+    li = cap tanh((zi + i_bias) / cap), lf = log_sigmoid(cap tanh((zf + f_bias) / cap)) and the running maximum
+    m_t = max(lf + m_(t-1), li) (``m_state`` [slots, H] float32, updated in place; 0 at a sequence's start), returns
+    float32 [tokens, H, 3]: exp(lf + m_(t-1) - m_t), exp(li - m_t), exp(-m_t)."""
+    _need(proj, "proj")
+    tokens, ld = proj.shape
+    _need(i_bias, "i_bias", torch.float32, (heads,))
+    _need(f_bias, "f_bias", torch.float32, (heads,))
+    _need(m_state, "m_state", torch.float32)
+    if m_state.dim() != 2 or m_state.shape[1] != heads:
+        raise KernelError(f"mlstm_gates: m_state {tuple(m_state.shape)} does not fit {heads} heads")
+    if max(i_col, f_col) + heads > ld:
+        raise KernelError("mlstm_gates: the projection is narrower than its columns")
+    seqs = seq_slot.numel()
+    _need(seq_slot, "seq_slot", torch.int32, (seqs,))
+    _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
+    gates = torch.empty((tokens, heads, 3), dtype=torch.float32, device=proj.device)
+    _call("mlstm", "ri_mlstm_gates", proj.data_ptr(), ld, int(i_col), int(f_col), i_bias.data_ptr(), f_bias.data_ptr(),
+          float(cap), m_state.data_ptr(), gates.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seqs, heads,
+          _code(proj.dtype), _stream())
+    return gates
+
+
+def scalar_decay_recurrent(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, gates: torch.Tensor, qscale: float,
+                           state: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, heads: int, dim: int,
+                           vdim: int, ones: bool = True, single: bool = False) -> torch.Tensor:
+    """The recurrence S <- a_t S + (b_t k_t) v_t^T, o_t = S^T (q_t qscale) per (sequence, head) with one decay a_t and
+    one key factor b_t per token and head: ``gates`` [tokens, H, >= 2] float32 holds them at [.., 0] and [.., 1].  With
+    ``ones`` the values get one more column that is 1 for every token: ``state`` is [slots, H, dim, vdim + 1] and the
+    result [tokens, H, vdim + 1], whose last column is n_t . q_t with n_t = a_t n_(t-1) + b_t k_t.  q, k, v are columns
+    of ``proj`` as for ``gla_recurrent``; the state is float32 and updated in place."""
+    _need(proj, "proj")
+    tokens, ld = proj.shape
+    _need(gates, "gates", torch.float32)
+    if gates.dim() != 3 or tuple(gates.shape[:2]) != (tokens, heads) or gates.shape[2] < 2:
+        raise KernelError(f"scalar_decay_recurrent: gates {tuple(gates.shape)} do not fit {tokens} tokens of {heads} heads")
+    wide = vdim + (1 if ones else 0)
+    _need(state, "state", torch.float32)
+    if tuple(state.shape[1:]) != (heads, dim, wide):
+        raise KernelError(f"scalar_decay_recurrent: state {tuple(state.shape)} does not fit {heads} heads of {dim} x {wide}")
+    seqs = seq_slot.numel()
+    _need(seq_slot, "seq_slot", torch.int32, (seqs,))
+    _need(seq_start, "seq_start", torch.int32, (seqs + 1,))
+    if max(q_col, k_col) + heads * dim > ld or v_col + heads * vdim > ld:
+        raise KernelError("scalar_decay_recurrent: the projection is narrower than its columns")
+    o = torch.empty((tokens, heads, wide), dtype=torch.float32, device=proj.device)
+    _call("gla", "ri_gla_recurrent_scalar", proj.data_ptr(), ld, int(q_col), int(k_col), int(v_col), gates.data_ptr(),
+          int(gates.shape[2]), 1 if ones else 0, float(qscale), state.data_ptr(), o.data_ptr(), seq_slot.data_ptr(),
+          seq_start.data_ptr(), seqs, heads, dim, vdim, 1 if single and tokens == seqs else 0, _code(proj.dtype), _stream())
+    return o
+
+
+def mlstm_head_norm_gate(o: torch.Tensor, gates: torch.Tensor, gain: torch.Tensor, eps: float, g: torch.Tensor,
+                         out_dtype: torch.dtype) -> torch.Tensor:
+    """Behind the matrix memory's recurrence: o [tokens, H, vdim + 1] float32 (last column n . q), ``gates``
+    [tokens, H, 3] (exp(-m) at [.., 2]).  h = o[.., :vdim] / (max(|n . q|, exp(-m)) + 1e-6), then per head
+    y = h / sqrt(mean(h^2) + eps) * gain[h, :] * sigmoid(g[t, h vdim ..]); ``gain`` [H vdim] float32; ``g`` [tokens,
+    H vdim] may be a block of columns of a wider matrix (float32 or the compute dtype).  Returns [tokens, H vdim]."""
+    _need(o, "o", torch.float32)
+    tokens, H, wide = o.shape
+    vdim = wide - 1
+    _need(gates, "gates", torch.float32, (tokens, H, 3))
+    _need(gain, "gain", torch.float32, (H * vdim,))
+    ldg = _columns(g, "g", g.dtype)
+    if tuple(g.shape) != (tokens, H * vdim):
+        raise KernelError(f"mlstm_head_norm_gate: gates {tuple(g.shape)} do not fit {tuple(o.shape)}")
+    y = torch.empty((tokens, H * vdim), dtype=out_dtype, device=o.device)
+    _call("mlstm", "ri_mlstm_head_norm_gate", o.data_ptr(), gates.data_ptr(), gain.data_ptr(), float(eps), g.data_ptr(), ldg,
+          y.data_ptr(), tokens, H, vdim, _code(g.dtype), _code(out_dtype), _stream())
     return y
 
 
@@ -659,7 +742,7 @@ def qk_norm_rope_append(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, he
 
 
 def rms_gains(resid: torch.Tensor, gains, eps: float, out_dtype: torch.dtype, terms=(), entry=None,
-              rows: Optional[torch.Tensor] = None, then: Optional[torch.Tensor] = None):
+              rows: Optional[torch.Tensor] = None, then: Optional[torch.Tensor] = None, post=None, out=None):
     """RMS norm of the float32 residual ``resid`` [n, dim] with one or two gains: a tuple of x / sqrt(mean(x^2) + eps) * g
     for every g of ``gains``, from one pass.  First whatever joins the residual, in float32: ``terms``, up to two pending
     outputs as pairs (tensor [n, dim] of the compute dtype, a float32 factor [1] or None for 1), two of them summed
@@ -667,12 +750,17 @@ def rms_gains(resid: torch.Tensor, gains, eps: float, out_dtype: torch.dtype, te
     table[ids] * scale (``ids`` None: not) and the vector ``vec`` [dim].  The new residual is written back unless ``rows``
     (int32 indices: only those rows are read, in that order) is given.  ``then``: the weight matrix of the linear that
     reads the first result next; for a handful of bfloat16 rows the kernel asks for its start to be brought into L2 (a
-    hint; it changes no result)."""
+    hint; it changes no result).
+
+    ``post`` (a pair (gain float32 [dim], eps)): the pending outputs' weighted sum s is normed on its own before it joins,
+    x + s / sqrt(mean(s^2) + eps) * gain (a norm behind the sublayer; the gain may hold a layer scale as well).
+    Without ``gains`` nothing is normed in front: whatever joins joins, the residual is written back, and ``out`` (if
+    given: the left ``dim`` columns of a wider matrix of the compute dtype) gets the new residual's rows; returns ()."""
     _need(resid, "resid", torch.float32)
     n, dim = resid.shape
     gains = tuple(gains)
-    if not 1 <= len(gains) <= 2:
-        raise KernelError(f"rms_gains: {len(gains)} gains (one or two)")
+    if len(gains) > 2 or (not gains and (rows is not None or then is not None)):
+        raise KernelError(f"rms_gains: {len(gains)} gains (one or two; none only for whole steps)")
     for g in gains:
         _need(g, "gain", torch.float32, (dim,))
     terms = list(terms)
@@ -702,27 +790,64 @@ def rms_gains(resid: torch.Tensor, gains, eps: float, out_dtype: torch.dtype, te
     n_out = n if rows is None else rows.numel()
     outs = tuple(torch.empty((n_out, dim), dtype=out_dtype, device=resid.device) for _ in gains)
     hint = _weight_hint(then, n_out) if out_dtype == torch.bfloat16 else None
-    _call("norm_gains", "ri_norm_gains", resid.data_ptr(), _ptr(terms[0][0]), _ptr(terms[0][1]), _ptr(terms[1][0]),
-          _ptr(terms[1][1]), _ptr(ids), _ptr(table), int(vocab), scale, _ptr(vec), _ptr(rows), gains[0].data_ptr(),
-          gains[1].data_ptr() if len(gains) > 1 else None, outs[0].data_ptr(), outs[1].data_ptr() if len(gains) > 1 else None,
-          n_out, dim, float(eps), _code(out_dtype), _ptr(hint), hint.shape[0] if hint is not None else 0,
-          hint.shape[1] if hint is not None else 0, error_flag(resid.device).data_ptr(), _stream())
+    post_gain, post_eps = (None, 0.0) if post is None else post
+    if post_gain is not None:
+        _need(post_gain, "gain of the norm behind the sublayer", torch.float32, (dim,))
+        if terms[0][0] is None:
+            raise KernelError("rms_gains: a norm behind the sublayer needs its output")
+    pitch = 0
+    if not gains and out is not None:
+        pitch = _columns(out, "out", out_dtype)
+        if tuple(out.shape) != (n, dim):
+            raise KernelError(f"rms_gains: out {tuple(out.shape)} does not fit {n} rows of {dim}")
+    first = gains[0].data_ptr() if gains else None
+    first_out = outs[0].data_ptr() if gains else (_ptr(out) if out is not None else None)
+    _call("norm_gains", "ri_norm_gains_post", resid.data_ptr(), _ptr(terms[0][0]), _ptr(terms[0][1]), _ptr(terms[1][0]),
+          _ptr(terms[1][1]), _ptr(ids), _ptr(table), int(vocab), scale, _ptr(vec), _ptr(rows), first,
+          gains[1].data_ptr() if len(gains) > 1 else None, first_out, outs[1].data_ptr() if len(gains) > 1 else None,
+          n_out, dim, float(eps), _ptr(post_gain), float(post_eps), int(pitch), _code(out_dtype), _ptr(hint),
+          hint.shape[0] if hint is not None else 0, hint.shape[1] if hint is not None else 0,
+          error_flag(resid.device).data_ptr(), _stream())
     return outs
+
+
+def embed_same(ids: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = table[ids[t]] in the table's own dtype; ``out`` [tokens, dim] may be a block of columns of a wider
+    matrix (one half of the input of a product over two concatenated vectors)."""
+    _need(ids, "ids", torch.int32)
+    _need(table, "table")
+    tokens, (vocab, dim) = ids.numel(), table.shape
+    pitch = _columns(out, "out", table.dtype)
+    if tuple(out.shape) != (tokens, dim):
+        raise KernelError(f"embed_same: out {tuple(out.shape)} does not fit {tokens} rows of {dim}")
+    _call("elementwise", "ri_embed_rows_same", ids.data_ptr(), table.data_ptr(), out.data_ptr(), int(pitch), tokens, dim, vocab,
+          _code(table.dtype), error_flag(table.device).data_ptr(), _stream())
 
 
 def qkv_prep(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, heads: int, kv_heads: int, Dp: int, Dk: int,
              bias: Optional[torch.Tensor], rope_table: Optional[torch.Tensor], rot: int, pairs: bool, unit: bool,
              eps: float, k_pool: Optional[torch.Tensor], v_pool: Optional[torch.Tensor], page_table: torch.Tensor,
-             tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor, write_kv: bool = True) -> torch.Tensor:
+             tok_seq: torch.Tensor, tok_pos: torch.Tensor, seq_slot: torch.Tensor, write_kv: bool = True,
+             norm: str = "", q_gain: Optional[torch.Tensor] = None, k_gain: Optional[torch.Tensor] = None,
+             norm_eps: float = 0.0) -> torch.Tensor:
     """Between the q/k/v product and the attention kernels: ``proj`` [tokens, N] holds the q heads from column ``q_col``,
     the k heads from ``k_col`` and the v heads from ``v_col`` (< 0: none, the values are the keys as cached), every head
     ``Dp`` columns wide with ``Dk`` true elements.  ``bias`` (float32, by column of the product) is added first; the first
     ``rot`` elements of q and k heads are turned by ``rope_table`` [positions, rot/2, 2] (``pairs``: partners are
     neighbours, else half a rotated part apart); with ``unit`` q and k heads are then divided by their root mean square
     over ``Dk`` (eps inside the root, no gain).  k (and v) go to the token's place in the pools
-    [pages, KV, page_size, Dp]; returns q [tokens, H, Dp].  All of it in float32."""
+    [pages, KV, page_size, Dp]; returns q [tokens, H, Dp].  All of it in float32.
+
+    ``norm``: an RMS norm of q and k before the rotation, "head" over each head's ``Dk`` elements with the gains
+    ``q_gain`` and ``k_gain`` [Dp] for all heads, or "all" over all q heads (all k heads) of the token at once with gains
+    [H, Dp] and [KV, Dp]; eps ``norm_eps`` inside the root; the gains' padding columns are zero."""
     _need(proj, "proj")
     tokens, ld = proj.shape
+    if norm not in ("", "head", "all"):
+        raise KernelError(f"qkv_prep: norm {norm!r} (head, all or none)")
+    if norm:
+        for g, name, n in ((q_gain, "q_gain", heads), (k_gain, "k_gain", kv_heads)):
+            _need(g, name, torch.float32, (Dp,) if norm == "head" else (n, Dp))
     nv = 0 if v_col < 0 else kv_heads
     if q_col + heads * Dp > ld or k_col + kv_heads * Dp > ld or (nv and v_col + nv * Dp > ld):
         raise KernelError("qkv_prep: the projection is narrower than its columns")
@@ -751,10 +876,11 @@ def qkv_prep(proj: torch.Tensor, q_col: int, k_col: int, v_col: int, heads: int,
     for t, n in ((tok_seq, "tok_seq"), (tok_pos, "tok_pos"), (seq_slot, "seq_slot")):
         _need(t, n, torch.int32)
     q = torch.empty((tokens, heads, Dp), dtype=proj.dtype, device=proj.device)
-    _call("qkv_prep", "ri_qkv_prep", proj.data_ptr(), ld, int(q_col), int(k_col), int(v_col), _ptr(bias), q.data_ptr(),
+    _call("qkv_prep", "ri_qkv_prep_norm", proj.data_ptr(), ld, int(q_col), int(k_col), int(v_col), _ptr(bias), q.data_ptr(),
           _ptr(k_pool) if write_kv else None, _ptr(v_pool) if write_kv and nv else None, page_table.data_ptr(),
           tok_seq.data_ptr(), tok_pos.data_ptr(), seq_slot.data_ptr(), _ptr(rope_table), rope_rows, int(rot),
-          1 if pairs else 0, 1 if unit else 0, float(eps), tokens, heads, kv_heads, Dp, Dk, page_table.shape[1], page_size,
+          1 if pairs else 0, 1 if unit else 0, float(eps), _ptr(q_gain) if norm else None, _ptr(k_gain) if norm else None,
+          {"": 0, "head": 1, "all": 2}[norm], float(norm_eps), tokens, heads, kv_heads, Dp, Dk, page_table.shape[1], page_size,
           pages, 1 if write_kv else 0, _code(proj.dtype), error_flag(proj.device).data_ptr(), _stream())
     return q
 
@@ -1124,10 +1250,19 @@ def linear_gated(x: torch.Tensor, w_gate_up: torch.Tensor, block: int, kind: str
     return gated_act(linear(x, w_gate_up), kind, block, limit, alpha)
 
 
-def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: int):
+MOE_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, top: int, score: str = "softmax",
+              groups: int = 1, keep: int = 1, group_top: int = 2, scale: float = 1.0, renormalize: bool = True):
     """Per token the ``top`` router outputs with the largest softmax(router x) + correction (ties: the lower index),
     and as weights their softmax scores divided by their sum (+ 1e-20).  ``router`` [N, D] and ``correction`` [N]
-    float32.  Returns (int32 [tokens, top], float32 [tokens, top])."""
+    float32.  Returns (int32 [tokens, top], float32 [tokens, top]).
+
+    ``score`` "sigmoid": the scores are the sigmoid of every output on its own.  ``groups`` > 1: the outputs form that
+    many equal runs of neighbours, a run's score is the sum of its ``group_top`` largest choice scores, and only outputs
+    of the ``keep`` best runs can be chosen.  The weights are multiplied by ``scale``; ``renormalize`` False leaves out
+    the division by their sum."""
     _need(x, "x")
     tokens, D = x.shape
     _need(router, "router", torch.float32)
@@ -1137,8 +1272,11 @@ def moe_route(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor, t
     _need(correction, "correction", torch.float32, (N,))
     idx = torch.empty((tokens, top), dtype=torch.int32, device=x.device)
     weight = torch.empty((tokens, top), dtype=torch.float32, device=x.device)
-    _call("moe", "ri_moe_route", x.data_ptr(), router.data_ptr(), correction.data_ptr(), idx.data_ptr(), weight.data_ptr(),
-          tokens, D, N, int(top), _code(x.dtype), _stream())
+    if score not in MOE_SCORES:
+        raise KernelError(f"moe_route: score {score!r} (known: {', '.join(sorted(MOE_SCORES))})")
+    _call("moe", "ri_moe_route_rule", x.data_ptr(), router.data_ptr(), correction.data_ptr(), idx.data_ptr(), weight.data_ptr(),
+          tokens, D, N, int(top), MOE_SCORES[score], int(groups), int(keep), int(group_top), float(scale),
+          1 if renormalize else 0, _code(x.dtype), _stream())
     return idx, weight
 
 

@@ -3,7 +3,7 @@ from .base import (BuildEnv, CacheRequest, FeedForward, Mixer, Norm, Part, Pendi
                    WeightedSum)
 from .registry import (ParamInfo, build_part, part_class, register_block, register_embedding, register_ffn,
                        register_head, register_link, register_mixer, register_norm, register_position, registered)
-from . import (attention, ends, gated_delta, gla, latent_attention, link, mlp, moe, norm, parallel,  # noqa: F401
+from . import (attention, ends, gated_delta, gla, latent_attention, link, mlp, mlstm, moe, norm, parallel,  # noqa: F401
                position)                                                      # (registers the built-in parts)
 from .block import BlockBase, build_block, norm_before
 

@@ -17,7 +17,9 @@ Further options of the record, each a field with its constants: biases on the q/
 (added in float32 by the kernel that rotates and appends), values that are the keys as cached
 (no v tensor, one pool), queries and keys divided by their root mean square AFTER the rotation
 (no gain), a soft-cap on the scores, and a sigmoid gate per output element from a projection of
-the mixer's input, stacked into the q/k/v product.  A record that uses any of them runs the
+the mixer's input (or one gate per head), stacked into the q/k/v product; a norm of queries and keys
+before the rotation that runs over the whole projection of a token instead of over each head.  A record
+that uses any of them (or a per-head norm together with values of another size) runs the
 "extended" order of work: one product for q, k, (v), (gate); ``ops.qkv_prep`` (bias, rotation,
 unit norm, append); attention; gate; output projection.  Heads are then always padded to a
 multiple of 16 elements, so that the tensor-core kernels take every size.
@@ -49,8 +51,9 @@ class Attention(Mixer):
         self.q_gain = self.k_gain = self.sink = None
         self.Dk, self.Dv = spec.head_dim, (spec.v_head_dim or spec.head_dim)
         self.Dp = self.Dk if self.Dk == self.Dv else -(-max(self.Dk, self.Dv) // 16) * 16
-        if self.Dp != self.Dk and spec.qk_norm is not None:
-            raise ValueError("a per-head norm of queries and keys with values of another size is not built")
+        self.norm_span = getattr(spec, "qk_norm_span", "head") if spec.qk_norm is not None else ""
+        if self.norm_span not in ("", "head", "all"):
+            raise ValueError(f"qk_norm_span {self.norm_span!r}: 'head' or 'all'")
         if spec.window and spec.chunk:
             raise ValueError("an attention layer has a window or a chunked mask, not both")
         self.rot = getattr(spec.position, "rot", None) or getattr(spec.position, "rotary_dim", 0)
@@ -63,15 +66,15 @@ class Attention(Mixer):
         self.gated = getattr(spec, "gate", "") or ""
         if getattr(spec, "values", "own") not in ("own", "keys"):
             raise ValueError(f"values {spec.values!r}: 'own' or 'keys'")
-        if self.gated not in ("", "element"):
-            raise ValueError(f"gate {self.gated!r} is not built (known: element)")
+        if self.gated not in ("", "element", "head"):
+            raise ValueError(f"gate {self.gated!r} is not built (known: element, head)")
         if set(self.bias_of) - {"q", "k", "v"}:
             raise ValueError(f"biases {self.bias_of}: of q, k, v")
-        self.extended = bool(self.bias_of or self.keys_are_values or self.unit_rms or self.softcap or self.gated)
+        self.extended = bool(self.bias_of or self.keys_are_values or self.unit_rms or self.softcap or self.gated
+                             or self.norm_span == "all" or (self.norm_span and self.Dp != self.Dk))
         if self.extended:
-            if spec.qk_norm is not None or spec.sink or spec.chunk:
-                raise ValueError("the extended attention options do not combine with a per-head norm before the "
-                                 "rotation, a sink or a chunked mask")
+            if spec.sink or spec.chunk:
+                raise ValueError("the extended attention options do not combine with a sink or a chunked mask")
             if self.keys_are_values and self.Dv != self.Dk:
                 raise ValueError(f"values that are the keys have the keys' size {self.Dk}, not {self.Dv}")
             self.Dp = -(-max(self.Dk, self.Dv) // 16) * 16
@@ -90,10 +93,12 @@ class Attention(Mixer):
             if which in (getattr(spec, "bias", ()) or ()) and name in infos:
                 infos[name + suffix] = ParamInfo(infos[name].shape[:1], "vector")
         if getattr(spec, "gate", ""):
-            infos[spec.gate_name] = ParamInfo((H * Dv, D))
+            infos[spec.gate_name] = ParamInfo((H if spec.gate == "head" else H * Dv, D))
         if spec.qk_norm is not None:
-            infos["q_norm.weight"] = ParamInfo((Dh,), "gain")
-            infos["k_norm.weight"] = ParamInfo((Dh,), "gain")
+            qn, kn = getattr(spec, "qk_norm_names", ("q_norm.weight", "k_norm.weight"))
+            whole = getattr(spec, "qk_norm_span", "head") == "all"
+            infos[qn] = ParamInfo((H * Dh if whole else Dh,), "gain")
+            infos[kn] = ParamInfo((KV * Dh if whole else Dh,), "gain")
         if spec.sink:
             infos[sink] = ParamInfo((H,), "vector")
         return infos
@@ -113,8 +118,14 @@ class Attention(Mixer):
         blocks = [rows(tensors[q], s.num_heads, self.Dk), rows(tensors[k], s.num_kv_heads, self.Dk)]
         if not self.keys_are_values:
             blocks.append(rows(tensors[v], s.num_kv_heads, self.Dv))
-        if self.gated:
+        if self.gated == "element":
             blocks.append(rows(tensors[s.gate_name], s.num_heads, self.Dv))
+        elif self.gated == "head":
+            # one row per head, then zero rows up to a multiple of 8: the product's rows stay whole 16-byte pieces
+            g = tensors[s.gate_name]
+            blocks.append(g)
+            if g.shape[0] % 8:
+                blocks.append(g.new_zeros((8 - g.shape[0] % 8, D)))
         self.qkv = torch.cat(blocks, dim=0).contiguous()
         if self.extended:
             # the columns of the product: q heads, k heads, v heads (unless the keys serve), gate; the biases as one
@@ -138,7 +149,19 @@ class Attention(Mixer):
             wo = padded.view(D, s.num_heads * Dp)
         self.o = wo.contiguous()
         if s.qk_norm is not None:
-            self.q_gain, self.k_gain = tensors["q_norm.weight"], tensors["k_norm.weight"]
+            qn, kn = getattr(s, "qk_norm_names", ("q_norm.weight", "k_norm.weight"))
+            self.q_gain, self.k_gain = tensors[qn], tensors[kn]
+            if self.extended:
+                # the kernel indexes the gains by the padded head's column: zeros in the padding
+                def padded(g, heads):
+                    if self.norm_span == "head":
+                        out = g.new_zeros((Dp,))
+                        out[:self.Dk] = g
+                    else:
+                        out = g.new_zeros((heads, Dp))
+                        out[:, :self.Dk] = g.view(heads, self.Dk)
+                    return out.contiguous()
+                self.q_gain, self.k_gain = padded(self.q_gain, s.num_heads), padded(self.k_gain, s.num_kv_heads)
         if s.sink:
             self.sink = tensors[sink]
 
@@ -168,7 +191,8 @@ class Attention(Mixer):
             q = ops.qkv_prep(proj, 0, self.k_col, self.v_col, H, KV, Dp, self.Dk, self.bias, table,
                              self.rot if table is not None else 0, getattr(self.position, "pairs", False),
                              self.unit_rms, s.unit_eps, cache.k_pool, cache.v_pool, cache.page_table, ctx.tok_seq,
-                             ctx.tok_pos, ctx.seq_slot, write_kv=cache.writes)
+                             ctx.tok_pos, ctx.seq_slot, write_kv=cache.writes, norm=self.norm_span, q_gain=self.q_gain,
+                             k_gain=self.k_gain, norm_eps=s.qk_norm.eps if s.qk_norm is not None else 0.0)
         fast = ops.fast_attention_supported(q.dtype, Dp, cache.page_size)
         with section("attention"):
             if fast and ctx.decode_only:
@@ -183,7 +207,7 @@ class Attention(Mixer):
                                     ctx.seq_len, ctx.max_new, self.scale, s.window, softcap=self.softcap)
         if self.gated:
             with section("attn gate"):
-                ops.gate_heads(out, proj[:, self.g_col:self.g_col + H * Dp], "sigmoid")
+                ops.gate_heads(out, proj[:, self.g_col:self.g_col + (H if self.gated == "head" else H * Dp)], "sigmoid")
         with section("attn o proj"):
             return ops.linear(out.view(T, H * Dp), self.o)
 

@@ -115,6 +115,9 @@ class Pending:
     more: tuple = ()
     # float32 terms that join after the outputs (an :class:`Injection`); ``y`` may then be None (nothing pending)
     entry: object = None
+    # a norm behind the sublayer, as a pair (gain float32 [width], eps): the outputs' weighted sum s joins as
+    # s / sqrt(mean(s^2) + eps) * gain (``out`` and the weights in ``more`` are then float32 factors [1])
+    post: object = None
 
 
 @dataclass

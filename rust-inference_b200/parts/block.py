@@ -119,6 +119,30 @@ class ParallelNormsBlock(BlockBase):
         return resid, self.link.pending(a, self.ffn(xs[1], ctx))
 
 
+@register_block("sandwich")
+class SandwichBlock(BlockBase):
+    """A norm in front of and behind each sublayer: x <- x + link1(mixer(norm1(x))), x <- x + link2(ffn(norm2(x))), the
+    links being norms with a layer scale (``post_norm`` in ``parts/link.py``).  The feed-forward half is optional.  As in
+    the other arrangements an output is left pending: the norm in front of the next sublayer norms it, scales it, adds
+    it and norms the new residual in one pass."""
+
+    @classmethod
+    def slots(cls, spec):
+        out = [("mixer_norm", "norm", spec.mixer_norm), ("mixer_link", "link", spec.mixer_link),
+               ("mixer", "mixer", spec.mixer)]
+        if spec.ffn is not None:
+            out += [("ffn_norm", "norm", spec.ffn_norm), ("ffn_link", "link", spec.ffn_link), ("ffn", "ffn", spec.ffn)]
+        return tuple(out)
+
+    def __call__(self, resid, delta, ctx, cache):
+        x = norm_before(self.mixer_norm, resid, delta, self.mixer)
+        delta = self.mixer_link.pending(self.mixer(x, ctx, cache))
+        if self.spec.ffn is None:
+            return resid, delta
+        x = norm_before(self.ffn_norm, resid, delta, self.ffn)
+        return resid, self.ffn_link.pending(self.ffn(x, ctx))
+
+
 def norm_before(norm, resid, delta, reader):
     """``norm(resid + delta)`` for the part ``reader``; a norm that takes hints is told which matrix is read next."""
     if norm.takes_hint:

@@ -2,6 +2,9 @@
 
     z = R h (float32),  s = softmax(z) over all router outputs,  choice = the ``top`` largest of s + correction
     w_j = s[choice_j] / (sum_j s[choice_j] + 1e-20)
+Options of the record: s = sigmoid(z) element by element; a choice only among the experts of the best groups of
+neighbouring experts (a group's score: the sum of its largest choice scores); weights that are not divided by their
+sum; a constant factor on the weights.
     y = sum_j w_j expert_{choice_j}(h)  (+ shared(h))
 The router's last ``identity`` outputs stand for experts that return h itself and have no tensors.  The experts are
 gated feed-forwards of one record (``parts/mlp.py``'s "gated" kind gives the formula); their matrices are stacked
@@ -33,6 +36,14 @@ class MixtureOfExperts(FeedForward):
             raise ValueError(f"experts of kind {getattr(spec.expert, 'kind', None)!r} are not built (known: gated)")
         if not 1 <= spec.top <= spec.experts + spec.identity:
             raise ValueError(f"top {spec.top} of {spec.experts} + {spec.identity} experts")
+        if getattr(spec, "score", "softmax") not in ops.MOE_SCORES:
+            raise ValueError(f"score {spec.score!r} is not built (known: {', '.join(sorted(ops.MOE_SCORES))})")
+        groups, keep = getattr(spec, "groups", 1), getattr(spec, "group_keep", 1)
+        outputs = spec.experts + spec.identity
+        if groups < 1 or outputs % groups or not 1 <= keep <= groups or getattr(spec, "group_top", 2) < 1:
+            raise ValueError(f"{outputs} router outputs in {groups} groups of which {keep} are kept")
+        if groups > 1 and spec.top > keep * (outputs // groups):
+            raise ValueError(f"top {spec.top} of the {keep * (outputs // groups)} outputs of the kept groups")
         self.shared = build_part("ffn", spec.shared, env) if spec.shared is not None else None
 
     @classmethod
@@ -64,7 +75,9 @@ class MixtureOfExperts(FeedForward):
         s, ex = self.spec, self.spec.expert
         T = x.shape[0]
         with section("moe router"):
-            idx, weight = ops.moe_route(x, self.router, self.correction, s.top)
+            idx, weight = ops.moe_route(x, self.router, self.correction, s.top, getattr(s, "score", "softmax"),
+                                        getattr(s, "groups", 1), getattr(s, "group_keep", 1), getattr(s, "group_top", 2),
+                                        getattr(s, "route_scale", 1.0), getattr(s, "renormalize", True))
             # many pairs per expert (a prompt): tiles of 64 rows, where the bfloat16 kernel for them takes the sizes
             wide = (x.dtype == torch.bfloat16 and T * s.top >= 48 * s.experts and s.hidden_size % 8 == 0
                     and ex.intermediate_size % 8 == 0)

@@ -73,16 +73,22 @@ class RMSGains(Norm):
     """RMS norm of the (single-stream) residual with one gain per name of the record: one pass computes
     1 / sqrt(mean(x^2) + eps) once and writes x times it times every gain.  The pending outputs (up to two, the sum of
     the two taken first: x + (a + b)) and the terms of a pass's entry (:class:`~.base.Injection`) join in the same
-    pass, in float32.  Returns one tensor for one name, a tuple for several."""
+    pass, in float32; outputs that come with a norm behind their sublayer (``Pending.post``) are normed on the way.
+    ``one_plus``: the tensors are stored around zero, the gains are 1 + tensor.  Returns one tensor for one name, a tuple
+    for several."""
     graph_safe = True
     takes_hint = True
 
     @classmethod
     def param_infos(cls, spec):
-        return {name: ParamInfo((spec.size,), "gain") for name in spec.names}
+        # gains that are stored around zero (``one_plus``) are drawn around zero in the random-weights mode as well
+        role = "vector" if getattr(spec, "one_plus", False) else "gain"
+        return {name: ParamInfo((spec.size,), role) for name in spec.names}
 
     def load(self, tensors):
         self.gains = tuple(tensors[name] for name in self.spec.names)
+        if getattr(self.spec, "one_plus", False):
+            self.gains = tuple((g + 1.0).contiguous() for g in self.gains)
         if not 1 <= len(self.gains) <= 2:
             raise ValueError(f"rms_gains: {len(self.gains)} gains (one or two are built)")
 
@@ -90,8 +96,9 @@ class RMSGains(Norm):
         return sum(g.numel() * 4 for g in self.gains)
 
     def __call__(self, resid, delta=None, rows=None, then=None):
-        terms, entry = [], None
+        terms, entry, post = [], None, None
         if isinstance(delta, Pending):
+            post = delta.post
             if delta.mix is not None:
                 raise ValueError("rms_gains reads a residual of one stream without mixing weights")
             if delta.y is not None:
@@ -104,5 +111,6 @@ class RMSGains(Norm):
                 raise ValueError("rms_gains reads a residual of one stream")
             resid = resid.view(resid.shape[0], resid.shape[2])
         with section("rmsnorm"):
-            outs = ops.rms_gains(resid, self.gains, self.spec.eps, self.env.dtype, terms=terms, entry=entry, rows=rows, then=then)
+            outs = ops.rms_gains(resid, self.gains, self.spec.eps, self.env.dtype, terms=terms, entry=entry, rows=rows,
+                                 then=then, post=post)
         return outs[0] if len(outs) == 1 else outs

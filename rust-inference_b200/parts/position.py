@@ -43,6 +43,9 @@ class Rope(PositionEncoding):
 
     def inv_freq(self) -> np.ndarray:
         rot = self.spec.rot
+        if getattr(self.spec, "freq64", False):
+            i = np.arange(rot // 2, dtype=np.float64)
+            return (float(self.spec.theta) ** (-2.0 * i / rot)).astype(np.float32)
         theta = np.float32(self.spec.theta)
         exps = np.arange(0, rot, 2, dtype=np.float32) / np.float32(rot)
         return (np.float32(1.0) / np.power(theta, exps, dtype=np.float32)).astype(np.float32)
@@ -50,7 +53,8 @@ class Rope(PositionEncoding):
     def prepare(self, max_positions: int) -> None:
         if self._table is not None and self._table.shape[0] >= max_positions:
             return
-        key = (str(self.env.device), int(self.spec.rot), float(np.float32(self.spec.theta)), float(self.spec.scaling))
+        key = (str(self.env.device), int(self.spec.rot), float(np.float32(self.spec.theta)), float(self.spec.scaling),
+               bool(getattr(self.spec, "freq64", False)), float(self.spec.theta))
         shared = _shared_tables.get(key)
         if shared is not None and shared.shape[0] >= max_positions:
             self._table = shared

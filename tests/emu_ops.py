@@ -15,7 +15,8 @@ import torch
 __all__ = ["embed", "rmsnorm", "add_rows", "silu_mul", "linear_swiglu", "linear", "qk_norm_rope_append", "attention", "argmax",
            "sample", "mark_seen", "stream_norm", "activation", "gate_heads", "linear_heads", "latent_prep", "gla_recurrent",
            "head_norm_gate", "linear_act", "scale_", "embed_pair_hash", "short_conv", "delta_rule_recurrent", "gated_act",
-           "linear_gated", "moe_route", "moe_plan", "moe_grouped_linear", "moe_combine", "rms_gains", "qkv_prep", "softcap_"]
+           "linear_gated", "moe_route", "moe_plan", "moe_grouped_linear", "moe_combine", "rms_gains", "qkv_prep", "softcap_",
+           "embed_same", "mlstm_gates", "scalar_decay_recurrent", "mlstm_head_norm_gate"]
 
 
 def embed(ids, table, scale=1.0, copies=1):
@@ -50,6 +51,8 @@ def activation(x, kind):
     f = x.float()
     if kind == "relu2":
         return (torch.clamp(f, min=0.0) ** 2).to(x.dtype)
+    if kind == "gelu":
+        return (0.5 * f * (1.0 + torch.erf(f / math.sqrt(2.0)))).to(x.dtype)
     return (0.5 * f * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (f + 0.044715 * f ** 3)))).to(x.dtype)
 
 
@@ -336,16 +339,29 @@ def linear_gated(x, w_gate_up, block, kind="silu", limit=0.0, alpha=1.0):
     return gated_act(linear(x, w_gate_up), kind, block, limit, alpha)
 
 
-def moe_route(x, router, correction, top):
-    s = torch.softmax(x.float() @ router.t(), dim=-1)
+def moe_route(x, router, correction, top, score="softmax", groups=1, keep=1, group_top=2, scale=1.0, renormalize=True):
+    z = x.float() @ router.t()
+    s = torch.softmax(z, dim=-1) if score == "softmax" else torch.sigmoid(z)
     c = s + correction
+    if groups > 1:
+        T, N = c.shape
+        size = N // groups
+        gs = torch.topk(c.view(T, groups, size), min(group_top, size), dim=-1).values.sum(-1)
+        kept = torch.zeros(T, groups, dtype=torch.bool)
+        for _ in range(keep):
+            at = torch.argmax(gs, dim=-1)
+            kept[torch.arange(T), at] = True
+            gs[torch.arange(T), at] = -math.inf
+        c = torch.where(kept[:, :, None].expand(T, groups, size).reshape(T, N), c, torch.full_like(c, -math.inf))
     idx = torch.zeros(x.shape[0], top, dtype=torch.int32)
     for j in range(top):
         at = torch.argmax(c, dim=-1)                    # the first of equals
         idx[:, j] = at.to(torch.int32)
         c[torch.arange(x.shape[0]), at] = -math.inf
     w = torch.gather(s, 1, idx.long())
-    return idx, w / (w.sum(-1, keepdim=True) + 1e-20)
+    if renormalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return idx, w * scale
 
 
 def moe_plan(idx, experts, wide=False):
@@ -384,12 +400,15 @@ def moe_combine(pair_out, idx, weight, x, experts, extra=None):
     return y.to(x.dtype)
 
 
-def rms_gains(resid, gains, eps, out_dtype, terms=(), entry=None, rows=None, then=None):
+def rms_gains(resid, gains, eps, out_dtype, terms=(), entry=None, rows=None, then=None, post=None, out=None):
     x = resid if rows is None else resid[rows.long()]
     terms = list(terms)
     if terms:
         ys = [(y if rows is None else y[rows.long()]).float() * (1.0 if w is None else w[0]) for y, w in terms]
-        x = x + (ys[0] if len(ys) == 1 else ys[0] + ys[1])
+        total = ys[0] if len(ys) == 1 else ys[0] + ys[1]
+        if post is not None and post[0] is not None:
+            total = total / torch.sqrt((total * total).mean(-1, keepdim=True) + post[1]) * post[0]
+        x = x + total
     if entry is not None:
         if entry.ids is not None:
             x = x + entry.table[entry.ids.long()].float() * entry.scale
@@ -397,12 +416,63 @@ def rms_gains(resid, gains, eps, out_dtype, terms=(), entry=None, rows=None, the
             x = x + entry.vec
     if rows is None and (terms or entry is not None):
         resid.copy_(x)
+    if not gains:
+        if out is not None:
+            out.copy_(x.to(out_dtype))
+        return ()
     r = 1.0 / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
     return tuple((x * r * g).to(out_dtype) for g in gains)
 
 
+def embed_same(ids, table, out):
+    out.copy_(table[ids.long()])
+
+
+def mlstm_gates(proj, i_col, f_col, i_bias, f_bias, cap, m_state, seq_slot, seq_start, heads):
+    p = proj.float()
+    li = cap * torch.tanh((p[:, i_col:i_col + heads] + i_bias) / cap)
+    lf = torch.nn.functional.logsigmoid(cap * torch.tanh((p[:, f_col:f_col + heads] + f_bias) / cap))
+    gates = torch.zeros(proj.shape[0], heads, 3)
+    for b in range(seq_slot.numel()):
+        m = m_state[int(seq_slot[b])]
+        for t in range(int(seq_start[b]), int(seq_start[b + 1])):
+            m_new = torch.maximum(lf[t] + m, li[t])
+            gates[t, :, 0] = torch.exp(lf[t] + m - m_new)
+            gates[t, :, 1] = torch.exp(li[t] - m_new)
+            gates[t, :, 2] = torch.exp(-m_new)
+            m.copy_(m_new)
+    return gates
+
+
+def scalar_decay_recurrent(proj, q_col, k_col, v_col, gates, qscale, state, seq_slot, seq_start, heads, dim, vdim, ones=True,
+                           single=False):
+    T = proj.shape[0]
+    p = proj.float()
+    q = p[:, q_col:q_col + heads * dim].view(T, heads, dim) * qscale
+    k = p[:, k_col:k_col + heads * dim].view(T, heads, dim)
+    v = p[:, v_col:v_col + heads * vdim].view(T, heads, vdim)
+    if ones:
+        v = torch.cat([v, torch.ones(T, heads, 1)], dim=-1)
+    o = torch.zeros(T, heads, v.shape[-1])
+    for b in range(seq_slot.numel()):
+        S = state[int(seq_slot[b])]
+        for t in range(int(seq_start[b]), int(seq_start[b + 1])):
+            S.copy_(gates[t, :, 0, None, None] * S + (gates[t, :, 1, None] * k[t])[:, :, None] * v[t][:, None, :])
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+    return o
+
+
+def mlstm_head_norm_gate(o, gates, gain, eps, g, out_dtype):
+    tokens, H, wide = o.shape
+    vdim = wide - 1
+    den = torch.maximum(o[..., vdim].abs(), gates[..., 2]) + 1e-6
+    h = o[..., :vdim] / den[..., None]
+    y = h / torch.sqrt((h * h).mean(-1, keepdim=True) + eps)
+    return (y.reshape(tokens, H * vdim) * gain * torch.sigmoid(g.float())).to(out_dtype)
+
+
 def qkv_prep(proj, q_col, k_col, v_col, heads, kv_heads, Dp, Dk, bias, rope_table, rot, pairs, unit, eps, k_pool, v_pool,
-             page_table, tok_seq, tok_pos, seq_slot, write_kv=True):
+             page_table, tok_seq, tok_pos, seq_slot, write_kv=True, norm="", q_gain=None, k_gain=None, norm_eps=0.0):
     T = proj.shape[0]
     x = proj.float()
     if bias is not None:
@@ -427,7 +497,14 @@ def qkv_prep(proj, q_col, k_col, v_col, heads, kv_heads, Dp, Dk, bias, rope_tabl
     def unit_rms(t):
         return t / torch.sqrt((t * t).sum(-1, keepdim=True) / Dk + eps) if unit else t
 
-    q, k = unit_rms(turn(q)), unit_rms(turn(k))
+    def normed(t, gain):
+        if norm == "head":
+            return t / torch.sqrt((t * t).sum(-1, keepdim=True) / Dk + norm_eps) * gain
+        if norm == "all":
+            return t / torch.sqrt((t * t).sum((-1, -2), keepdim=True) / (Dk * t.shape[1]) + norm_eps) * gain
+        return t
+
+    q, k = unit_rms(turn(normed(q, q_gain))), unit_rms(turn(normed(k, k_gain)))
     if write_kv:
         P = k_pool.shape[2]
         for t in range(T):

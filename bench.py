@@ -18,12 +18,14 @@ steps end at exactly 4,096 tokens.  One JSON line is printed:
   points     decode tokens a second at batch 1 and 64 (device-timed), and the same through
              the Python entry point (e2e_b1, e2e_b64)
 
-    python bench.py --design ranudra|pitenex|kagatar [--size small|large]
+    python bench.py --design ranudra|pitenex|kagatar|puratar [--size small|large]
 
 measures another design (Ranudra: latent attention, gated linear attention, hyper-connections; Pitenex: chunked attention
 with a sink beside the gated delta rule, dense and routed feed-forwards; Kagatar: three kinds of attention with biases
-beside a clamped-swish feed-forward behind two gains over one RMS statistic) at layer sizes that
-resemble a real model's, beside a Qwen3 model of the same width and depth: decode at batch 8 and a
+beside a clamped-swish feed-forward behind two gains over one RMS statistic; Puratar: norms in front of and behind every
+sublayer, attention with a gate per head or beside the matrix memory of xLSTM, dense and routed feed-forwards) at layer
+sizes that resemble a real model's, beside a Qwen3 model of the same width and depth (Puratar: beside the Pitenex model
+of the same width and depth, the closest design): decode at batch 8 and a
 prompt step of 2,048 tokens, device-timed, and the device time of every section of both steps from eager runs with
 the section timers on, with the bytes or flops of the sections that have a roofline.  One JSON line.
 
@@ -326,7 +328,30 @@ def kagatar_config(z) -> dict:
             "layers": [gated, capped, shared] * (z["layers"] // 3)}
 
 
-DESIGNS = {"ranudra": ranudra_config, "pitenex": pitenex_config, "kagatar": kagatar_config}
+def puratar_config(z) -> dict:
+    """Layers with a norm in front of and behind each sublayer that alternate a mixer of attention (biases, a norm over
+    the whole projection) beside the matrix memory (heads of 128 x 128, half as many as the attention has) with a dense
+    gelu feed-forward, and attention with per-head norms and a gate per head with a routed feed-forward (16 experts in 4
+    groups of which 2 are kept, 4 per token, a shared expert); heads of 128, four query heads per key/value head, rotation
+    of half a head.  The first two layers are a run of one pass (its entry projects the residual beside the embedding's
+    output and adds the learned vector)."""
+    D, H = z["width"], z["heads"]
+    G = max(1, H // 4)
+    inter = -(-(2 * z["ff"] // 3) // 256) * 256          # three matrices of a gated feed-forward against two
+    attn = {"heads": H, "kv_heads": G, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "rot": {"base": 500000.0, "dims": 64}}
+    right = {"heads": max(1, H // 2), "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    both = {"type": "parallel", "mixer": {"left": attn, "right": right, "left_scale": 0.7, "right_scale": 0.7},
+            "mlp": {"kind": "dense", "ff": z["ff"]}}
+    routed = {"type": "attention", "mixer": attn,
+              "mlp": {"kind": "moe", "router": {"experts": 16, "top": 4, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+                      "expert": {"ff": inter // 8}, "shared": {"ff": inter // 4}}}
+    return {"architecture": "Puratar", "vocab": z["vocab"], "width": D, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+            "loop": {"start": 0, "stop": 2, "times": 1}, "layers": [both, routed] * (z["layers"] // 2)}
+
+
+DESIGNS = {"ranudra": ranudra_config, "pitenex": pitenex_config, "kagatar": kagatar_config, "puratar": puratar_config}
+# the model that a design is measured beside, where it is not the Qwen3 model of equal size: the closest design
+BESIDE = {"puratar": "pitenex"}
 
 
 def qwen3_like(z) -> dict:
@@ -353,7 +378,8 @@ def run_design(a) -> int:
     clocks.start()
     windows = []
     out = {}
-    for label, cfg in ((a.design, DESIGNS[a.design](z)), ("qwen3", qwen3_like(z))):
+    other = BESIDE.get(a.design, "qwen3")
+    for label, cfg in ((a.design, DESIGNS[a.design](z)), (other, DESIGNS[other](z) if other in DESIGNS else qwen3_like(z))):
         t_model = time.time()
         model = Model.from_random(cfg, seed=1, dtype="bfloat16", device=dev)
         V = model.spec.vocab_size
@@ -439,9 +465,9 @@ def run_design(a) -> int:
         "ms_per_step": r["decode_ms_per_step"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random-init weights, uniform random token ids", "design": a.design,
         "config": dict(z, size=a.size, global_batch=B, seq_len=ctx, prefill_tokens=T, parallelism="1 GPU", peaks=peak_src,
-                       beside="a Qwen3 model of the same width and depth (weight_bytes of both are given)"),
+                       beside=f"a {other.capitalize()} model of the same width and depth (weight_bytes of both are given)"),
         "peaks": {"hbm_gbs": hbm_gbs, "bf16_tflops": bf16_tflops},
-        a.design: r, "qwen3": out["qwen3"], "clocks": clocks.summary(windows), "gpu_launches": r["decode_launches"] * K,
+        a.design: r, other: out[other], "clocks": clocks.summary(windows), "gpu_launches": r["decode_launches"] * K,
         "impl": "ours",
     }
     print(json.dumps(line))

@@ -600,6 +600,27 @@ __global__ void gate_heads_vec8_kernel(T* __restrict__ x, const T* __restrict__ 
     o.store(x + 8 * i);
 }
 
+// a gate per head, eight neighbouring elements of one head per thread; the gate's formula is the one-element kernel's
+template <typename T>
+__global__ void gate_heads_vec8_head_kernel(T* __restrict__ x, const T* __restrict__ g, long long ldg, int heads, int width8,
+                                            int fn, size_t total8) {
+    pdl_trigger();
+    pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total8) return;
+    const size_t unit = i / width8;                     // (token, head)
+    const size_t t = unit / heads;
+    const int h = (int)(unit - t * heads);
+    const float z = ld_f(g + t * ldg + h);
+    const float s = 1.0f / (1.0f + expf(-z));
+    const float f = fn == 1 ? z * s : s;
+    Pack8<T> a, o;
+    a.load(x + 8 * i);
+#pragma unroll
+    for (int j = 0; j < 4; j++) o.set2(j, a.get(2 * j) * f, a.get(2 * j + 1) * f);
+    o.store(x + 8 * i);
+}
+
 extern "C" int ri_gate_heads(void* x, const void* g, long long ldg, int tokens, int heads, int width, int per_head, int fn,
                              int dtype, cudaStream_t stream) {
     if (tokens == 0) return 0;
@@ -613,6 +634,14 @@ extern "C" int ri_gate_heads(void* x, const void* g, long long ldg, int tokens, 
         const unsigned blocks8 = (unsigned)((total8 + 255) / 256);
         if (dtype == RI_DTYPE_F32) ri_launch_pdl(gate_heads_vec8_kernel<float>, dim3(blocks8), dim3(256), 0, stream, (float*)x, (const float*)g, ldg, per_tok8, fn, total8);
         else ri_launch_pdl(gate_heads_vec8_kernel<__nv_bfloat16>, dim3(blocks8), dim3(256), 0, stream, (__nv_bfloat16*)x, (const __nv_bfloat16*)g, ldg, per_tok8, fn, total8);
+        RI_CHECK_LAUNCH("gate_heads");
+        return 0;
+    }
+    if (per_head && width % 8 == 0 && ((uintptr_t)x & 15) == 0 && (dtype == RI_DTYPE_F32 || dtype == RI_DTYPE_BF16)) {
+        const size_t total8 = total / 8;
+        const unsigned blocks8 = (unsigned)((total8 + 255) / 256);
+        if (dtype == RI_DTYPE_F32) ri_launch_pdl(gate_heads_vec8_head_kernel<float>, dim3(blocks8), dim3(256), 0, stream, (float*)x, (const float*)g, ldg, heads, width / 8, fn, total8);
+        else ri_launch_pdl(gate_heads_vec8_head_kernel<__nv_bfloat16>, dim3(blocks8), dim3(256), 0, stream, (__nv_bfloat16*)x, (const __nv_bfloat16*)g, ldg, heads, width / 8, fn, total8);
         RI_CHECK_LAUNCH("gate_heads");
         return 0;
     }

@@ -68,13 +68,80 @@ mlstm_gates_kernel(const T* __restrict__ proj, long long ld, int i_col, int f_co
     if (lane == 0) m_state[(size_t)slot * H + h] = m;
 }
 
+// The same for prompts: a block of ML_BLOCK threads per (sequence, head) takes ML_BLOCK tokens at a time: every thread its
+// token's li and lf, then ONE thread the chain over them from shared memory (the same operations in the same order as in
+// the kernel above: the same bits), then every thread its token's three results.
+#define ML_BLOCK 256
+template <typename T>
+__global__ void __launch_bounds__(ML_BLOCK)
+mlstm_gates_block_kernel(const T* __restrict__ proj, long long ld, int i_col, int f_col, const float* __restrict__ i_bias,
+                         const float* __restrict__ f_bias, float cap, float* __restrict__ m_state, float* __restrict__ gates,
+                         const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int H) {
+    __shared__ float s_li[ML_BLOCK], s_lf[ML_BLOCK], s_before[ML_BLOCK], s_mine[ML_BLOCK];
+    __shared__ float s_m;
+    pdl_trigger();
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int t0 = seq_start[b], t1 = seq_start[b + 1];
+    const int slot = seq_slot[b];
+    const float bi = i_bias[h], bf = f_bias[h];
+    pdl_wait();
+    if (threadIdx.x == 0) s_m = m_state[(size_t)slot * H + h];
+    for (int base = t0; base < t1; base += ML_BLOCK) {
+        const int t = base + threadIdx.x;
+        float li = 0.0f, lf = 0.0f;
+        if (t < t1) {
+            const T* row = proj + (size_t)t * ld;
+            li = cap * tanhf((ld_f(row + i_col + h) + bi) / cap);
+            lf = ml_log_sigmoid(cap * tanhf((ld_f(row + f_col + h) + bf) / cap));
+        }
+        s_li[threadIdx.x] = li;
+        s_lf[threadIdx.x] = lf;
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float m = s_m;
+            const int n = min(ML_BLOCK, t1 - base);
+            for (int g = 0; g < n; g++) {
+                const float m_new = fmaxf(s_lf[g] + m, s_li[g]);
+                s_before[g] = m;
+                s_mine[g] = m_new;
+                m = m_new;
+            }
+            s_m = m;
+        }
+        __syncthreads();
+        if (t < t1) {
+            const float m_before = s_before[threadIdx.x], m_mine = s_mine[threadIdx.x];
+            float* out = gates + ((size_t)t * H + h) * 3;
+            out[0] = expf(lf + m_before - m_mine);
+            out[1] = expf(li - m_mine);
+            out[2] = expf(-m_mine);
+        }
+        // (the next round's first barrier stands between these reads and the chain's next writes)
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) m_state[(size_t)slot * H + h] = s_m;
+}
+
 // proj [tokens, ld] of the type `dtype`; i and f pre-activations of head h at columns i_col + h and f_col + h;
 // gates [tokens, H, 3] float32 out.
+// single: every sequence brings one token (a warp per sequence and head); else a block per sequence and head.
 extern "C" int ri_mlstm_gates(const void* proj, long long ld, int i_col, int f_col, const float* i_bias, const float* f_bias,
                               float cap, float* m_state, float* gates, const int* seq_slot, const int* seq_start, int seqs,
-                              int H, int dtype, cudaStream_t stream) {
+                              int H, int single, int dtype, cudaStream_t stream) {
     if (seqs == 0) return 0;
     RI_REQUIRE(seqs > 0 && seqs <= 65535 && H > 0 && cap > 0.0f, "mlstm_gates: bad sizes (seqs %d, heads %d, cap %g)", seqs, H, cap);
+    if (!single) {
+        const dim3 bgrid(H, seqs);
+        if (dtype == RI_DTYPE_F32)
+            ri_launch_pdl(mlstm_gates_block_kernel<float>, bgrid, dim3(ML_BLOCK), 0, stream, (const float*)proj, ld, i_col, f_col,
+                          i_bias, f_bias, cap, m_state, gates, seq_slot, seq_start, H);
+        else if (dtype == RI_DTYPE_BF16)
+            ri_launch_pdl(mlstm_gates_block_kernel<__nv_bfloat16>, bgrid, dim3(ML_BLOCK), 0, stream, (const __nv_bfloat16*)proj, ld,
+                          i_col, f_col, i_bias, f_bias, cap, m_state, gates, seq_slot, seq_start, H);
+        else RI_FAIL(-1, "mlstm_gates: unknown dtype %d", dtype);
+        RI_CHECK_LAUNCH("mlstm_gates");
+        return 0;
+    }
     const dim3 grid((H + ML_WARPS - 1) / ML_WARPS, seqs);
     if (dtype == RI_DTYPE_F32)
         ri_launch_pdl(mlstm_gates_kernel<float>, grid, dim3(32 * ML_WARPS), 0, stream, (const float*)proj, ld, i_col, f_col, i_bias,

@@ -30,7 +30,7 @@ _SIGNATURES = {
     ("qkv_prep", "ri_qkv_prep_norm"): [_P, _L, _I, _I, _I] + [_P] * 9 + [_I, _I, _I, _I, _F, _P, _P, _I, _F] + [_I] * 10 + [_P, _P],
     ("moe", "ri_moe_route_rule"): [_P, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _I, _F, _I, _I, _P],
     ("gla", "ri_gla_recurrent_scalar"): [_P, _L, _I, _I, _I, _P, _I, _I, _F, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
-    ("mlstm", "ri_mlstm_gates"): [_P, _L, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _P],
+    ("mlstm", "ri_mlstm_gates"): [_P, _L, _I, _I, _P, _P, _F, _P, _P, _P, _P, _I, _I, _I, _I, _P],
     ("mlstm", "ri_mlstm_head_norm_gate"): [_P, _P, _P, _F, _P, _L, _P, _I, _I, _I, _I, _I, _P],
     ("elementwise", "ri_gate_heads"): [_P, _P, _L, _I, _I, _I, _I, _I, _I, _P],
     ("streams", "ri_stream_norm"): [_P] * 8 + [_I, _I, _I, _F, _I, _I, _P],
@@ -429,12 +429,14 @@ def head_norm_gate(o: torch.Tensor, gain: torch.Tensor, eps: float, g: torch.Ten
 
 
 def mlstm_gates(proj: torch.Tensor, i_col: int, f_col: int, i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float,
-                m_state: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, heads: int) -> torch.Tensor:
+                m_state: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor, heads: int,
+                single: bool = False) -> torch.Tensor:
     """The gates of the matrix memory for the step's new tokens.  ``proj`` [tokens, N] holds the input gate's
     pre-activation of head h at column ``i_col`` + h and the forget gate's at ``f_col`` + h.  With
     li = cap tanh((zi + i_bias) / cap), lf = log_sigmoid(cap tanh((zf + f_bias) / cap)) and the running maximum
     m_t = max(lf + m_(t-1), li) (``m_state`` [slots, H] float32, updated in place; 0 at a sequence's start), returns
-    float32 [tokens, H, 3]: exp(lf + m_(t-1) - m_t), exp(li - m_t), exp(-m_t)."""
+    float32 [tokens, H, 3]: exp(lf + m_(t-1) - m_t), exp(li - m_t), exp(-m_t).  ``single``: every sequence brings one
+    token (another shape of kernel; the same bits)."""
     _need(proj, "proj")
     tokens, ld = proj.shape
     _need(i_bias, "i_bias", torch.float32, (heads,))
@@ -450,7 +452,7 @@ def mlstm_gates(proj: torch.Tensor, i_col: int, f_col: int, i_bias: torch.Tensor
     gates = torch.empty((tokens, heads, 3), dtype=torch.float32, device=proj.device)
     _call("mlstm", "ri_mlstm_gates", proj.data_ptr(), ld, int(i_col), int(f_col), i_bias.data_ptr(), f_bias.data_ptr(),
           float(cap), m_state.data_ptr(), gates.data_ptr(), seq_slot.data_ptr(), seq_start.data_ptr(), seqs, heads,
-          _code(proj.dtype), _stream())
+          1 if single and tokens == seqs else 0, _code(proj.dtype), _stream())
     return gates
 
 

@@ -81,7 +81,7 @@ class MatrixMemory(Mixer):
             proj = ops.linear(x, self.proj, out_dtype=torch.float32)
         with section("mlstm gates"):
             gates = ops.mlstm_gates(proj, self.i_col, self.f_col, self.i_bias, self.f_bias, s.gate_cap, cache.more_state[0],
-                                    ctx.seq_slot, ctx.seq_start, H)
+                                    ctx.seq_slot, ctx.seq_start, H, single=ctx.decode_only)
         with section("mlstm recurrence"):
             o = ops.scalar_decay_recurrent(proj, self.q_col, self.k_col, self.v_col, gates, s.dim ** -0.5, cache.state,
                                            ctx.seq_slot, ctx.seq_start, H, s.dim, s.vdim, ones=True, single=ctx.decode_only)

@@ -428,7 +428,7 @@ def embed_same(ids, table, out):
     out.copy_(table[ids.long()])
 
 
-def mlstm_gates(proj, i_col, f_col, i_bias, f_bias, cap, m_state, seq_slot, seq_start, heads):
+def mlstm_gates(proj, i_col, f_col, i_bias, f_bias, cap, m_state, seq_slot, seq_start, heads, single=False):
     p = proj.float()
     li = cap * torch.tanh((p[:, i_col:i_col + heads] + i_bias) / cap)
     lf = torch.nn.functional.logsigmoid(cap * torch.tanh((p[:, f_col:f_col + heads] + f_bias) / cap))

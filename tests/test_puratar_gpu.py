@@ -213,7 +213,7 @@ def test_matrix_memory_whole_in_pieces_and_token_by_token(H, d, dv, dtype):
         ys, at = [], 0
         for c in cuts:
             part, gp = proj_t[at:at + c].contiguous(), g[at:at + c].contiguous()
-            gates = ops.mlstm_gates(part, i_col, f_col, _t(ib), _t(fb), cap, m, _i([slot]), _i([0, c]), H)
+            gates = ops.mlstm_gates(part, i_col, f_col, _t(ib), _t(fb), cap, m, _i([slot]), _i([0, c]), H, single=(c == 1))
             o = ops.scalar_decay_recurrent(part, 0, H * d, 2 * H * d, gates, d ** -0.5, S, _i([slot]), _i([0, c]), H, d, dv,
                                            ones=True, single=(c == 1))
             ys.append(ops.mlstm_head_norm_gate(o, gates, _t(gain), eps, gp, dtype))
@@ -262,6 +262,21 @@ def test_exact_gelu_behind_a_product(dtype):
         _close(ops.linear_act(x, w, "gelu"), P.gelu_erf(z), dtype, f"{n} tokens", tol32=1e-5, tol16=1.2e-2)
     z = _t(np.linspace(-6, 6, 801), dtype)
     _close(ops.activation(z, "gelu"), P.gelu_erf(_np(z)), dtype, "the function alone", tol32=1e-6, tol16=5e-3)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("heads, width", [(6, 96), (3, 12), (16, 128), (1, 8)])
+def test_one_gate_per_head(heads, width, dtype):
+    """A sigmoid gate per head from columns of a wider matrix: eight elements per thread where a head is whole 16-byte
+    pieces, one otherwise."""
+    from rust_inference_b200 import ops
+    rng = np.random.default_rng(heads + width)
+    T = 37
+    x = _t(rng.standard_normal((T, heads, width)), dtype)
+    wide = _t(rng.standard_normal((T, 24 + heads)) * 3, dtype)
+    want = _np(x) * P.sigmoid(_np(wide)[:, 8:8 + heads])[:, :, None]
+    ops.gate_heads(x, wide[:, 8:8 + heads], "sigmoid")
+    _close(x, want, dtype, "gated heads", tol32=1e-6, tol16=5e-3)
 
 
 # ---- whole models ------------------------------------------------------------------------------------------------------------

@@ -77,7 +77,7 @@ __global__ void __launch_bounds__(ML_BLOCK)
 mlstm_gates_block_kernel(const T* __restrict__ proj, long long ld, int i_col, int f_col, const float* __restrict__ i_bias,
                          const float* __restrict__ f_bias, float cap, float* __restrict__ m_state, float* __restrict__ gates,
                          const int* __restrict__ seq_slot, const int* __restrict__ seq_start, int H) {
-    __shared__ float s_li[ML_BLOCK], s_lf[ML_BLOCK], s_before[ML_BLOCK], s_mine[ML_BLOCK];
+    __shared__ __align__(16) float s_li[ML_BLOCK], s_lf[ML_BLOCK], s_before[ML_BLOCK], s_mine[ML_BLOCK];
     __shared__ float s_m;
     pdl_trigger();
     const int h = blockIdx.x, b = blockIdx.y;
@@ -98,15 +98,29 @@ mlstm_gates_block_kernel(const T* __restrict__ proj, long long ld, int i_col, in
         s_lf[threadIdx.x] = lf;
         __syncthreads();
         if (threadIdx.x == 0) {
+            // eight tokens' gates into registers at a time, so that only the additions and maxima form the chain
             float m = s_m;
             const int n = min(ML_BLOCK, t1 - base);
-            for (int g = 0; g < n; g++) {
-                const float m_new = fmaxf(s_lf[g] + m, s_li[g]);
-                s_before[g] = m;
-                s_mine[g] = m_new;
-                m = m_new;
+            for (int g0 = 0; g0 < n; g0 += 8) {
+                const float4 fa = *reinterpret_cast<const float4*>(s_lf + g0), fb = *reinterpret_cast<const float4*>(s_lf + g0 + 4);
+                const float4 ia = *reinterpret_cast<const float4*>(s_li + g0), ib = *reinterpret_cast<const float4*>(s_li + g0 + 4);
+                const float f8[8] = {fa.x, fa.y, fa.z, fa.w, fb.x, fb.y, fb.z, fb.w};
+                const float i8[8] = {ia.x, ia.y, ia.z, ia.w, ib.x, ib.y, ib.z, ib.w};
+                float before[8], mine[8];
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    // (tokens past the step's end hold li = lf = 0 and are computed too; their results are not read,
+                    // and m is taken from the last real token below)
+                    before[j] = m;
+                    m = fmaxf(f8[j] + m, i8[j]);
+                    mine[j] = m;
+                }
+                *reinterpret_cast<float4*>(s_before + g0) = make_float4(before[0], before[1], before[2], before[3]);
+                *reinterpret_cast<float4*>(s_before + g0 + 4) = make_float4(before[4], before[5], before[6], before[7]);
+                *reinterpret_cast<float4*>(s_mine + g0) = make_float4(mine[0], mine[1], mine[2], mine[3]);
+                *reinterpret_cast<float4*>(s_mine + g0 + 4) = make_float4(mine[4], mine[5], mine[6], mine[7]);
             }
-            s_m = m;
+            s_m = s_mine[n - 1];
         }
         __syncthreads();
         if (t < t1) {

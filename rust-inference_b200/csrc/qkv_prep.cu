@@ -69,6 +69,12 @@ __device__ __forceinline__ void qp_whole_norms(const QpArgs& a, const T* row, fl
     inv_k = a.KV ? 1.0f / sqrtf(sk / (float)(a.KV * a.Dk) + a.norm_eps) : 1.0f;
 }
 
+// the same with eight elements per load, for rows of whole 16-byte pieces (every thread's partial sums are added in a
+// fixed order: by thread, then over the block)
+template <typename T> struct Qp8;
+template <typename T>
+__device__ __forceinline__ void qp_whole_norms8(const QpArgs& a, const T* row, float* red, float& inv_q, float& inv_k);
+
 // any sizes: a warp per head, lanes strided over the head, the head staged in shared memory
 template <typename T>
 __global__ void qkv_prep_kernel(QpArgs a) {
@@ -183,6 +189,32 @@ template <> struct Qp8<__nv_bfloat16> {
     }
 };
 
+template <typename T>
+__device__ __forceinline__ void qp_whole_norms8(const QpArgs& a, const T* row, float* red, float& inv_q, float& inv_k) {
+    float sq = 0.0f, sk = 0.0f;
+    for (int which = 0; which < 2; which++) {
+        const int col0 = which ? a.k_col : a.q_col, n8 = (which ? a.KV : a.H) * a.Dp / 8;
+        float acc = 0.0f;
+        for (int i = threadIdx.x; i < n8; i += blockDim.x) {
+            float x[8];
+            Qp8<T>::load(row + col0 + 8 * i, x);
+            if (a.bias) {
+                float b[8];
+                Qp8<float>::load(a.bias + col0 + 8 * i, b);
+#pragma unroll
+                for (int j = 0; j < 8; j++) x[j] += b[j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) acc += x[j] * x[j];
+        }
+        if (which) sk = acc; else sq = acc;
+    }
+    sq = block_sum(sq, red);
+    sk = block_sum(sk, red);
+    inv_q = a.H ? 1.0f / sqrtf(sq / (float)(a.H * a.Dk) + a.norm_eps) : 1.0f;
+    inv_k = a.KV ? 1.0f / sqrtf(sk / (float)(a.KV * a.Dk) + a.norm_eps) : 1.0f;
+}
+
 // Partners half a rotated part apart (`pairs` 0) live in another lane of the head's group, rot / 16 lanes away (rot is
 // then a multiple of 16, so that a lane's eight elements lie on one side); a lane fetches them by shuffles.
 template <typename T>
@@ -242,7 +274,7 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
     const int heads_total = H + KV + (a.v_col >= 0 ? KV : 0);
     const T* row = (const T*)a.proj + (size_t)t * a.ld;
     float inv_q = 1.0f, inv_k = 1.0f;
-    if (a.norm == 2) qp_whole_norms<T>(a, row, red, inv_q, inv_k);
+    if (a.norm == 2) qp_whole_norms8<T>(a, row, red, inv_q, inv_k);
     const int stride = QP_WARPS * hpw * gridDim.y;
     for (int h0 = (blockIdx.y * QP_WARPS + warp) * hpw; h0 < heads_total; h0 += stride) {
         const int h = h0 + sub;
@@ -360,7 +392,8 @@ extern "C" int ri_qkv_prep_norm(const void* proj, long long ld, int q_col, int k
         const int per_block = QP_WARPS * (32 / group);
         int hb = (heads_total + per_block - 1) / per_block;
         if ((long long)tokens * hb > 4096) hb = 1 > 4096 / tokens ? 1 : 4096 / tokens;
-        if (norm == 2) hb = 1;                      // the block adds up the token's whole projection once
+        // (norm 2: every block of a token adds up the token's whole q and k projections for itself, in the same order,
+        // so the blocks of a token agree bit for bit; the rows come from L2)
         RI_REQUIRE(hb <= 65535, "qkv_prep: bad grid");
         dim3 grid(tokens, hb);
         if (dtype == RI_DTYPE_F32) ri_launch_pdl(qkv_prep_vec_kernel<float>, grid, dim3(32 * QP_WARPS), 0, stream, a, group);
@@ -370,7 +403,6 @@ extern "C" int ri_qkv_prep_norm(const void* proj, long long ld, int q_col, int k
     }
     int hb = (heads_total + QP_WARPS - 1) / QP_WARPS;
     if ((long long)tokens * hb > 4096) hb = 1 > 4096 / tokens ? 1 : 4096 / tokens;
-    if (norm == 2) hb = 1;
     RI_REQUIRE(hb <= 65535, "qkv_prep: bad grid");
     dim3 grid(tokens, hb);
     if (dtype == RI_DTYPE_F32) ri_launch_pdl(qkv_prep_kernel<float>, grid, dim3(32 * QP_WARPS), 0, stream, a);

@@ -7,7 +7,7 @@ are kept, and a router without groups that takes one expert and has no shared ex
 repeated run, no factor on the logits, a width that is no multiple of 8, one key/value head for all query heads, a memory
 whose heads have more key channels than the register kernel takes, experts in two groups of which one is kept.  C: head
 sizes of 64 and 128 (the tensor-core kernels and the vectorised preparation kernel), one layer at the start repeated
-twice, a memory with 96 key channels.
+twice, a memory with 96 key channels.  D: sizes that are multiples of nothing.
 
 Weights are made here, with activations of order one (so that attention is far from uniform and a missing norm, bias,
 gate or entry term shows), rounded to bfloat16 and stored as bfloat16.
@@ -83,7 +83,18 @@ CFG_C = {
         single(attn(8, 1, 64, 128, scale=0.2, rot=(500.0, 16)), moe(4, 2, 1.0, 48, groups=(2, 2))),
     ],
 }
-ALL = {"A": CFG_A, "B": CFG_B, "C": CFG_C}
+# D: nothing is a multiple of 4: a width of 50, heads of 10 and 6 elements, seven heads, five experts; one layer in the
+# middle repeated twice
+CFG_D = {
+    "architecture": "Puratar", "vocab": 83, "width": 50, "norm": {"eps": 3e-6}, "logit_scale": 0.6,
+    "loop": {"start": 1, "stop": 2, "times": 2},
+    "layers": [
+        single(attn(7, 7, 10, 6, rot=(40.0, 6)), dense(30)),
+        double(attn(3, 1, 14, 18, scale=0.3, rot=(900.0, 14)), memory(5, 10, 6, 3.0), 0.5, 0.5, moe(5, 2, 1.25, 14, shared=10)),
+        single(attn(1, 1, 22, 22, rot=(10.0, 2)), moe(9, 3, 0.5, 10, groups=(3, 1))),
+    ],
+}
+ALL = {"A": CFG_A, "B": CFG_B, "C": CFG_C, "D": CFG_D}
 
 
 def _bf16(a):

@@ -108,7 +108,7 @@ def test_plain_route_takes_groups_and_leaves_the_correction_out_of_the_weights()
     assert chosen == [2, 3]
 
 
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_three_ways_matches_plain(tmp_path, emulated_ops, name):
     d, config, weights = K.make_model_dir(tmp_path, name, seed=3)
     rng = np.random.default_rng(4)

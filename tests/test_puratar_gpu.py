@@ -294,7 +294,7 @@ def _portions(reqs, sizes):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_in_five_cuttings_matches_plain(tmp_path, name, dtype):
     d, config, weights = K.make_model_dir(tmp_path, name, seed=3)
     rng = np.random.default_rng(4)

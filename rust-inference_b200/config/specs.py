@@ -30,7 +30,7 @@ class RMSGainsSpec:
     """One RMS statistic, several gains: y_k = x / sqrt(mean(x^2) + eps) * gain_k for every name in ``names`` (the
     gains' local tensor names; an empty name is the norm's prefix alone).  The sublayers of a layer that all read
     the same residual through norms of their own get their inputs from one pass over it.  ``one_plus``: the tensors
-    are stored around zero and the gain is 1 + tensor."""
+    hold the gains minus one: the gain is 1 + tensor."""
     size: int
     eps: float
     names: Tuple[str, ...] = ("",)
@@ -296,7 +296,7 @@ class HyperConnectionSpec:
 class PostNormSpec:
     """How a sublayer's output joins a single-stream residual when a norm stands BEHIND the sublayer:
     x <- x + scale * (y / sqrt(mean(y^2) + eps) * gain), y the sublayer's output (a weighted sum of several outputs is
-    taken first).  ``gain_name``: the gain's tensor; ``one_plus``: it is stored around zero (gain = 1 + tensor);
+    taken first).  ``gain_name``: the gain's tensor; ``one_plus``: it holds the gain minus one (gain = 1 + tensor);
     ``scale_name``: a vector of the residual's size that multiplies the normed output element by element (a layer
     scale), "" for none."""
     size: int

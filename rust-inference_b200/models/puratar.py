@@ -1,6 +1,6 @@
 """Puratar: a decoder whose layers have a norm in front of and behind each sublayer and a layer scale,
-x <- x + ls1 * n1b(mixer(n1(x))), x <- x + ls2 * n2b(ff(n2(x))), all norms RMS norms whose weights are stored around
-zero (gain 1 + w).  The mixers are grouped-query attention with a per-head RMS norm of queries and keys, rotation of
+x <- x + ls1 * n1b(mixer(n1(x))), x <- x + ls2 * n2b(ff(n2(x))), all norms RMS norms whose tensors hold the gain
+minus one (gain 1 + w).  The mixers are grouped-query attention with a per-head RMS norm of queries and keys, rotation of
 half-apart partners on a part of a head and one sigmoid gate per head ("attention"), or two mixers side by side
 ("parallel"): attention with biases and an RMS norm over the whole query (key) projection, beside the matrix memory of
 xLSTM.  Feed-forwards are dense (exact gelu) or routed (sigmoid scores, a correction on the choice only, a choice

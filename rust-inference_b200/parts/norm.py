@@ -74,14 +74,14 @@ class RMSGains(Norm):
     1 / sqrt(mean(x^2) + eps) once and writes x times it times every gain.  The pending outputs (up to two, the sum of
     the two taken first: x + (a + b)) and the terms of a pass's entry (:class:`~.base.Injection`) join in the same
     pass, in float32; outputs that come with a norm behind their sublayer (``Pending.post``) are normed on the way.
-    ``one_plus``: the tensors are stored around zero, the gains are 1 + tensor.  Returns one tensor for one name, a tuple
+    ``one_plus``: the tensors hold the gains minus one, the gains are 1 + tensor.  Returns one tensor for one name, a tuple
     for several."""
     graph_safe = True
     takes_hint = True
 
     @classmethod
     def param_infos(cls, spec):
-        # gains that are stored around zero (``one_plus``) are drawn around zero in the random-weights mode as well
+        # tensors that hold a gain minus one (``one_plus``) are drawn near 0 in the random-weights mode as well
         role = "vector" if getattr(spec, "one_plus", False) else "gain"
         return {name: ParamInfo((spec.size,), role) for name in spec.names}
 

@@ -22,7 +22,7 @@ def rms_unit(x, eps):
 
 
 def norm_one_plus(x, w, eps):
-    """RMS norm whose weight is stored around zero."""
+    """RMS norm whose tensor w holds the gain minus one."""
     return rms_unit(x, eps) * (1.0 + w)
 
 

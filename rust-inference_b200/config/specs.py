@@ -506,7 +506,8 @@ class ModelSpec:
     # tensors of the embedding or the head whose names do not derive from ``embedding_name`` / ``head_name``:
     # (local name, full name) pairs
     end_names: Tuple[Tuple[str, str], ...] = ()
-    # what a pass over a repeated run of layers adds on entry (a :class:`PassEntrySpec`; None: nothing); the
+    # what a pass over a repeated run of layers does on entry (a :class:`PassEntrySpec`: terms that are added; a
+    # :class:`PassMixSpec`: a projection of the residual beside the embedding's output; None: nothing); the
     # schedule entries with ``enters`` >= 0 say where
     pass_entry: object = None
 

@@ -217,7 +217,9 @@ __device__ __forceinline__ void qp_whole_norms8(const QpArgs& a, const T* row, f
 
 // Partners half a rotated part apart (`pairs` 0) live in another lane of the head's group, rot / 16 lanes away (rot is
 // then a multiple of 16, so that a lane's eight elements lie on one side); a lane fetches them by shuffles.
-template <typename T>
+// PAIRS (partners are neighbours, or nothing is turned at all) and NORM (the norm before the rotation: 0, 1, 2) are
+// template parameters, so that a variant holds only its own angles and gains in registers.
+template <typename T, bool PAIRS, int NORM>
 __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
     __shared__ float red[33];
     pdl_trigger();
@@ -237,7 +239,7 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
     for (int j = 0; j < 4; j++) {
         cs_c[j] = 1.0f;
         cs_s[j] = 0.0f;
-        if (a.rope && a.pairs && rope_ok && live_lane && d0 + 2 * j < a.rot) {
+        if (PAIRS && a.rope && rope_ok && live_lane && d0 + 2 * j < a.rot) {
             const float2 c = a.rope[(size_t)pos * (a.rot / 2) + d0 / 2 + j];
             cs_c[j] = c.x;
             cs_s[j] = c.y;
@@ -245,7 +247,7 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
     }
     // halves: this lane's eight angles, the side it is on (the sine's sign) and how far away its partners are
     const int half = a.rot / 2;
-    const bool turns = a.rope && !a.pairs && live_lane && d0 < a.rot;
+    const bool turns = !PAIRS && a.rope && live_lane && d0 < a.rot;
     const bool upper = d0 >= half;
     float hc[8], hs[8];
 #pragma unroll
@@ -262,7 +264,7 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
     float gq[8], gk[8];
 #pragma unroll
     for (int j = 0; j < 8; j++) gq[j] = gk[j] = 1.0f;
-    if (a.norm == 1 && live_lane) {
+    if (NORM == 1 && live_lane) {
         if (a.q_gain) Qp8<float>::load(a.q_gain + d0, gq);
         if (a.k_gain) Qp8<float>::load(a.k_gain + d0, gk);
     }
@@ -274,7 +276,7 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
     const int heads_total = H + KV + (a.v_col >= 0 ? KV : 0);
     const T* row = (const T*)a.proj + (size_t)t * a.ld;
     float inv_q = 1.0f, inv_k = 1.0f;
-    if (a.norm == 2) qp_whole_norms8<T>(a, row, red, inv_q, inv_k);
+    if (NORM == 2) qp_whole_norms8<T>(a, row, red, inv_q, inv_k);
     const int stride = QP_WARPS * hpw * gridDim.y;
     for (int h0 = (blockIdx.y * QP_WARPS + warp) * hpw; h0 < heads_total; h0 += stride) {
         const int h = h0 + sub;
@@ -297,9 +299,9 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
             else if (page >= 0)
                 dst = (T*)(which == 1 ? a.k_pool : a.v_pool) + (((size_t)page * KV + hh) * a.page_size + pos % a.page_size) * Dp + d0;
         }
-        if (a.norm) {
+        if (NORM) {
             float ninv = which == 0 ? inv_q : inv_k;
-            if (a.norm == 1) {
+            if (NORM == 1) {
                 float ss = 0.0f;
 #pragma unroll
                 for (int j = 0; j < 8; j++) ss += x[j] * x[j];
@@ -308,7 +310,7 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
             }
             if (which < 2) {
                 float g8[8];
-                if (a.norm == 2) {
+                if (NORM == 2) {
                     Qp8<float>::load((which == 0 ? a.q_gain : a.k_gain) + (size_t)hh * Dp + d0, g8);
                 } else {
 #pragma unroll
@@ -318,7 +320,7 @@ __global__ void qkv_prep_vec_kernel(QpArgs a, int group) {
                 for (int j = 0; j < 8; j++) x[j] = x[j] * ninv * g8[j];
             }
         }
-        if (a.rope && !a.pairs) {
+        if (!PAIRS) {
             // every lane takes part in the shuffles; a lane that does not turn keeps its own values (cos 1, sin 0)
 #pragma unroll
             for (int j = 0; j < 8; j++) {
@@ -396,8 +398,21 @@ extern "C" int ri_qkv_prep_norm(const void* proj, long long ld, int q_col, int k
         // so the blocks of a token agree bit for bit; the rows come from L2)
         RI_REQUIRE(hb <= 65535, "qkv_prep: bad grid");
         dim3 grid(tokens, hb);
-        if (dtype == RI_DTYPE_F32) ri_launch_pdl(qkv_prep_vec_kernel<float>, grid, dim3(32 * QP_WARPS), 0, stream, a, group);
-        else ri_launch_pdl(qkv_prep_vec_kernel<__nv_bfloat16>, grid, dim3(32 * QP_WARPS), 0, stream, a, group);
+        const bool as_pairs = pairs || !rope_table;          // nothing to turn: the variant without shuffles
+#define QP_VEC(T, P, N) ri_launch_pdl(qkv_prep_vec_kernel<T, P, N>, grid, dim3(32 * QP_WARPS), 0, stream, a, group)
+#define QP_VEC_BY_NORM(T, P)                                 \
+        do {                                                 \
+            if (norm == 0) QP_VEC(T, P, 0);                  \
+            else if (norm == 1) QP_VEC(T, P, 1);             \
+            else QP_VEC(T, P, 2);                            \
+        } while (0)
+        if (dtype == RI_DTYPE_F32) {
+            if (as_pairs) QP_VEC_BY_NORM(float, true); else QP_VEC_BY_NORM(float, false);
+        } else {
+            if (as_pairs) QP_VEC_BY_NORM(__nv_bfloat16, true); else QP_VEC_BY_NORM(__nv_bfloat16, false);
+        }
+#undef QP_VEC_BY_NORM
+#undef QP_VEC
         RI_CHECK_LAUNCH("qkv_prep");
         return 0;
     }
